@@ -1,0 +1,94 @@
+/*
+ * Inner boundary: the C-ABI launch shim between the C++ host layer and the
+ * sm_100a CUDA kernels.  The reference isolates its device code the same way,
+ * behind `extern "C" void ..._kernel_do(raw pointers, POD tiling, stream)`
+ * launchers that never synchronise and report nothing; the host detects an
+ * enqueue failure by clearing and then peeking the runtime's last error
+ * (reference: sparse/spmv/arch35/spmv_host.cpp:564-575,617-629).
+ *
+ * Every pointer below is a CUDA device pointer unless it is marked "host";
+ * `stream` is a cudaStream_t.
+ */
+#ifndef ACLSPARSE_B200_KERNELS_H_
+#define ACLSPARSE_B200_KERNELS_H_
+
+#include <stdint.h>
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Per-launch parameters of the SpMV kernels.  Counterpart of the reference's
+ * SpmvArch35TilingData (sparse/spmv/arch35/spmv_tiling_data.h:38-68), passed
+ * by value as a kernel argument instead of being published to the workspace. */
+typedef struct AclspSpmvParams {
+    uint32_t rows;
+    uint32_t cols;
+    uint32_t nnz;
+    uint32_t indexBase;      /* subtracted from every column index */
+    int64_t colIndStride;    /* element strides of the CSR arrays and vectors */
+    int64_t valuesStride;
+    int64_t xStride;
+    int64_t yStride;
+    float alpha;             /* used when alphaPtr == NULL (host pointer mode) */
+    float beta;
+    const float* alphaPtr;   /* device pointer mode: scalars are read on the device */
+    const float* betaPtr;
+} AclspSpmvParams;
+
+/* Per-launch parameters of the SpMM kernels.  Counterpart of the reference's
+ * SpmmTilingWireV1 (sparse/spmm/arch35/spmm_tiling_wire.h:23-74). */
+typedef struct AclspSpmmParams {
+    uint32_t rows;           /* m: rows of A and C */
+    uint32_t cols;           /* k: columns of A, rows of op(B) */
+    uint32_t nnz;
+    uint32_t indexBase;
+    uint32_t n;              /* columns of C */
+    uint32_t opB;            /* 0: B is k x n, 1: B is n x k and read transposed */
+    uint32_t orderB;         /* 0 row-major, 1 column-major */
+    uint32_t orderC;
+    int64_t ldb;
+    int64_t ldc;
+    float alpha;
+    float beta;
+    const float* alphaPtr;
+    const float* betaPtr;
+} AclspSpmmParams;
+
+/* Builds the SpMV plan in `workspace`: header, base-0 row offsets, merge-path
+ * tile splits and per-tile row bins.  Replaces spmv_arch35_preprocess_kernel_do
+ * (reference: sparse/spmv/arch35/spmv_kernel.h:10-17, spmv_kernel.cpp:1165-1171),
+ * which only normalises the row offsets on one core. */
+void spmv_b200_preprocess_kernel_do(const void* rowPtr, void* workspace, uint32_t rows, uint32_t cols,
+                                    uint32_t nnz, int32_t indexBase, int64_t rowOffsetsStride, void* stream);
+
+/* y = alpha * A * x + beta * y over the plan in `workspace`.  Replaces
+ * spmv_arch35_kernel_do (reference: sparse/spmv/arch35/spmv_kernel.cpp:1173-1184). */
+void spmv_b200_kernel_do(const void* colInd, const void* values, const void* x, void* y, void* workspace,
+                         const AclspSpmvParams* params, void* stream);
+
+/* Builds the SpMM plan in `workspace`.  Replaces the host-side row reorder of
+ * the reference (sparse/spmm/arch35/host/spmm_csr_mat.cpp:180-210), which
+ * copies the row offsets to the host, sorts and copies a permutation back. */
+void spmm_b200_preprocess_kernel_do(const void* rowPtr, void* workspace, uint32_t rows, uint32_t cols,
+                                    uint32_t nnz, uint32_t denseCols, int32_t indexBase, void* stream);
+
+/* C = alpha * A * op(B) + beta * C over the plan in `workspace`.  Replaces
+ * spmm_kernel_launch (reference: sparse/spmm/arch35/kernel/spmm_kernel.h:18-31,
+ * spmm_kernel.cpp:265-309). */
+void spmm_b200_kernel_do(const void* colInd, const void* values, const void* b, void* c, void* workspace,
+                         const AclspSpmmParams* params, void* stream);
+
+/* Row-block boundaries that split the non-zeros evenly over `parts` devices:
+ * bounds[g] = min{ r : rowPtr[r] - base >= ceil(g * nnz / parts) }, g = 0..parts.
+ * `bounds` is a device array of parts+1 int32.  No counterpart in the
+ * reference, which is single-device. */
+void aclsp_b200_row_block_bounds_kernel_do(const void* rowPtr, uint32_t rows, uint32_t nnz, int32_t indexBase,
+                                           uint32_t parts, void* bounds, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* ACLSPARSE_B200_KERNELS_H_ */

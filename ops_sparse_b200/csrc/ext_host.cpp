@@ -1,0 +1,38 @@
+/*
+ * Host side of the B200-only entry points (include/aclsparse_b200_ext.h).
+ */
+#include <cuda_runtime.h>
+
+#include "aclsparse_b200_ext.h"
+#include "aclsparse_b200_kernels.h"
+#include "internal.h"
+
+extern "C" aclsparseStatus_t aclsparseB200RowBlockBounds(aclsparseHandle_t handle, aclsparseConstSpMatDescr_t matA,
+                                                         int parts, void* bounds)
+{
+    if (handle == nullptr) {
+        return ACL_SPARSE_STATUS_HANDLE_IS_NULLPTR;
+    }
+    if (handle->signature != kHandleSignature || handle->stream == nullptr) {
+        return ACL_SPARSE_STATUS_INVALID_VALUE;
+    }
+    if (matA == nullptr || matA->signature != kSpMatSignature || bounds == nullptr || parts < 1 || parts > 65535) {
+        return ACL_SPARSE_STATUS_INVALID_VALUE;
+    }
+    if (matA->format != ACL_SPARSE_FORMAT_CSR || matA->ptrType != ACL_SPARSE_INDEX_32I || matA->ptrStride != 1 ||
+        matA->rows > 0x7FFFFFFFull || matA->nnz > 0x7FFFFFFFull) {
+        return ACL_SPARSE_STATUS_NOT_SUPPORTED;
+    }
+    if (matA->rows > 0 && matA->ptrs == nullptr) {
+        return ACL_SPARSE_STATUS_INVALID_VALUE;
+    }
+    (void)cudaGetLastError();
+    aclsp_b200_row_block_bounds_kernel_do(matA->ptrs, static_cast<uint32_t>(matA->rows),
+                                          static_cast<uint32_t>(matA->nnz), static_cast<int32_t>(matA->baseType),
+                                          static_cast<uint32_t>(parts), bounds, handle->stream);
+    if (cudaPeekAtLastError() != cudaSuccess) {
+        ACLSP_LOGE("aclsparseB200RowBlockBounds", "kernel enqueue failed");
+        return ACL_SPARSE_STATUS_EXECUTION_FAILED;
+    }
+    return ACL_SPARSE_STATUS_SUCCESS;
+}

@@ -1,0 +1,15 @@
+/* Internal: launcher of the plan-building kernels (plan_kernels.cu). */
+#ifndef ACLSPARSE_B200_PLAN_KERNELS_H_
+#define ACLSPARSE_B200_PLAN_KERNELS_H_
+
+#include <cstdint>
+
+#include <cuda_runtime.h>
+
+// kind: ACLSP_KIND_SPMV or ACLSP_KIND_SPMM (plan_layout.h); denseCols is the
+// width of C for SpMM and 1 for SpMV.
+void AclspLaunchPlanBuild(const void* rowPtr, void* workspace, uint32_t rows, uint32_t cols, uint32_t nnz,
+                          int32_t indexBase, int64_t rowOffsetsStride, uint32_t kind, uint32_t denseCols,
+                          cudaStream_t stream);
+
+#endif  // ACLSPARSE_B200_PLAN_KERNELS_H_

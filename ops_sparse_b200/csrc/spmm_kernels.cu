@@ -1,0 +1,510 @@
+/*
+ * CSR SpMM for sm_100a:  C = alpha * A * op(B) + beta * C,  fp32, int32 indices.
+ *
+ * No tensor cores: at 16-32 non-zeros per row the product is a gather of rows
+ * of B, bound by memory, not a dense contraction.
+ *
+ * Work decomposition.  As for SpMV the matrix is cut along the merge path of
+ * (row ends, non-zeros), here into tiles of 1024 items, one CTA per tile, and
+ * the CTA cuts its tile once more the same way into eight 128-item pieces, one
+ * per warp.  A warp therefore streams at most 128 non-zeros whatever the row
+ * lengths are: a 500 000-entry row is spread over thousands of warps and a run
+ * of empty rows costs as much as a run of non-zeros.
+ *   1. The CTA stages the tile's column indices and values in shared memory
+ *      with coalesced 128-bit loads (evict-first).
+ *   2. Each warp walks its non-zeros in order.  For every non-zero the lanes
+ *      copy one row of B (a 32*VW-column panel of it) into the warp's ring of
+ *      shared-memory stages with cp.async, kStages rows ahead of the FMAs, so
+ *      eight row gathers per warp are in flight while earlier rows are
+ *      multiplied.  A lane reads back only the bytes it copied itself, so the
+ *      ring needs no barrier, only cp.async.wait_group.
+ *   3. At a row end the accumulators are written as alpha*acc + beta*C.  The
+ *      piece of a row that a warp shares with its neighbours goes to shared
+ *      memory and is combined in warp order; the pieces a tile shares with its
+ *      neighbours go to the plan's carry area and are combined in tile order
+ *      by a second kernel.  All orders are fixed: results are reproducible.
+ *
+ * Layouts.  VW in {4, 2, 1} floats per lane is the widest vector the operands
+ * allow (unit column stride of op(B) and C, leading dimensions and base
+ * addresses aligned to the vector).  VW = 1 addresses both matrices through
+ * (row stride, column stride) pairs and so also covers column-major B / C and
+ * op(B) = transpose.
+ *
+ * Out-of-range input never faults: offsets are clamped and entries whose
+ * column falls outside [0, k) are skipped (reference:
+ * sparse/spmm/arch35/kernel/spmm_kernel_simt.cpp:406-434 clamps alike).
+ */
+#include <cstdint>
+
+#include <cuda_runtime.h>
+
+#include "aclsparse_b200_kernels.h"
+#include "plan_layout.h"
+
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kWarps = kThreads / 32;
+constexpr int kTile = ACLSP_SPMM_TILE_ITEMS;
+constexpr int kWarpItems = kTile / kWarps;
+constexpr int kStages = 8;
+
+struct SpmmPlanView {
+    const int32_t* rowPtr;
+    int32_t* tileRow;
+    float* carry;  // [numTiles][2][n]: tail carry-out, head partial
+    uint32_t numTiles;
+};
+
+inline SpmmPlanView MakeView(void* workspace, uint32_t rows, uint32_t nnz, uint32_t n)
+{
+    AclspPlanLayout l;
+    aclspSpmmLayout(rows, nnz, n, &l);
+    auto* base = static_cast<unsigned char*>(workspace);
+    SpmmPlanView v;
+    v.rowPtr = reinterpret_cast<const int32_t*>(base + l.rowPtrOff);
+    v.tileRow = reinterpret_cast<int32_t*>(base + l.tileRowOff);
+    v.carry = reinterpret_cast<float*>(base + l.carryOff);
+    v.numTiles = l.numTiles;
+    return v;
+}
+
+// Element (r, c) of op(B) is B[r * bRow + c * bCol]; the same for C.
+struct DenseStrides {
+    int64_t bRow;
+    int64_t bCol;
+    int64_t cRow;
+    int64_t cCol;
+};
+
+__device__ __forceinline__ int ClampOffset(int v, int nnz)
+{
+    return v < 0 ? 0 : (v > nnz ? nnz : v);
+}
+
+template <int VW>
+struct Vec;
+template <>
+struct Vec<4> {
+    using T = float4;
+};
+template <>
+struct Vec<2> {
+    using T = float2;
+};
+template <>
+struct Vec<1> {
+    using T = float;
+};
+
+template <int BYTES>
+__device__ __forceinline__ void CpAsync(void* smem, const void* gmem)
+{
+    const unsigned dst = static_cast<unsigned>(__cvta_generic_to_shared(smem));
+    asm volatile("cp.async.ca.shared.global [%0], [%1], %2;\n" ::"r"(dst), "l"(gmem), "n"(BYTES) : "memory");
+}
+
+__device__ __forceinline__ void CpAsyncCommit()
+{
+    asm volatile("cp.async.commit_group;\n" ::: "memory");
+}
+
+template <int N>
+__device__ __forceinline__ void CpAsyncWait()
+{
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
+}
+
+struct Scalars {
+    float alpha;
+    float beta;
+    bool betaZero;
+};
+
+__device__ __forceinline__ Scalars LoadScalars(const AclspSpmmParams& p)
+{
+    Scalars s;
+    s.alpha = p.alphaPtr != nullptr ? *p.alphaPtr : p.alpha;
+    s.beta = p.betaPtr != nullptr ? *p.betaPtr : p.beta;
+    s.betaZero = s.beta == 0.0f;
+    return s;
+}
+
+// Merge-path split of a tile held in shared memory: rows of the tile that end
+// before local diagonal d.  sOff[k + 1] is the local end offset of row k.
+__device__ __forceinline__ int LocalMergeRow(const int* sOff, int nr, int nt, int d)
+{
+    int lo = d > nt ? d - nt : 0;
+    int hi = d < nr ? d : nr;
+    while (lo < hi) {
+        const int mid = (lo + hi) >> 1;
+        if (sOff[mid + 1] <= d - 1 - mid) {
+            lo = mid + 1;
+        } else {
+            hi = mid;
+        }
+    }
+    return lo;
+}
+
+constexpr size_t SmemBytes(int vw)
+{
+    return sizeof(int) * (kTile + 2)                    // sOff
+           + sizeof(int) * kTile                        // sCol
+           + sizeof(float) * kTile                      // sVal
+           + sizeof(float) * kWarps * kStages * 32 * vw // ring
+           + sizeof(float) * 2 * kWarps * 32 * vw       // warp tail / head
+           + sizeof(int) * (2 * kWarps + 2);            // warp row split, head flags
+}
+
+template <int VW>
+__global__ void __launch_bounds__(kThreads)
+SpmmTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ values, const float* __restrict__ B,
+               float* __restrict__ C, SpmmPlanView plan, AclspSpmmParams p, DenseStrides ds)
+{
+    using V = typename Vec<VW>::T;
+    constexpr int kPanel = 32 * VW;
+
+    extern __shared__ __align__(16) unsigned char smemRaw[];
+    float* sRing = reinterpret_cast<float*>(smemRaw);                 // [kWarps][kStages][kPanel]
+    float* sTail = sRing + kWarps * kStages * kPanel;                 // [kWarps][kPanel]
+    float* sHead = sTail + kWarps * kPanel;                           // [kWarps][kPanel]
+    float* sVal = sHead + kWarps * kPanel;                            // [kTile]
+    int* sCol = reinterpret_cast<int*>(sVal + kTile);                 // [kTile], -1 marks a skipped entry
+    int* sOff = sCol + kTile;                                         // [kTile + 2]
+    int* sWarpRow = sOff + kTile + 2;                                 // [kWarps + 1] first local row of each warp
+    int* sHasHead = sWarpRow + kWarps + 1;                            // [kWarps]
+
+    const int tid = threadIdx.x;
+    const int lane = tid & 31;
+    const int warp = tid >> 5;
+    const int t = blockIdx.x;
+    const int nnz = static_cast<int>(p.nnz);
+    const int n = static_cast<int>(p.n);
+    const int64_t total = static_cast<int64_t>(p.rows) + nnz;
+    int64_t d0 = static_cast<int64_t>(t) * kTile;
+    int64_t d1 = d0 + kTile;
+    d0 = d0 < total ? d0 : total;
+    d1 = d1 < total ? d1 : total;
+    const int i0 = plan.tileRow[t];
+    const int i1 = plan.tileRow[t + 1];
+    const int j0 = static_cast<int>(d0 - i0);
+    const int j1 = static_cast<int>(d1 - i1);
+    const int nr = i1 - i0;
+    const int nt = j1 - j0;
+    float* tileTail = plan.carry + static_cast<size_t>(2 * t) * n;
+    float* tileHead = tileTail + n;
+    if (nr < 0 || nt < 0 || nr + nt > kTile || i0 < 0 || i1 > static_cast<int>(p.rows) || j0 < 0 || j1 > nnz) {
+        for (int c = tid; c < 2 * n; c += kThreads) {  // inconsistent row offsets: contribute nothing
+            tileTail[c] = 0.0f;
+        }
+        return;
+    }
+
+    // Stage the tile: local row offsets, column indices (base 0) and values.
+    for (int k = tid; k <= nr; k += kThreads) {
+        sOff[k] = ClampOffset(plan.rowPtr[i0 + k], nnz) - j0;
+    }
+    {
+        const bool vector = (reinterpret_cast<uintptr_t>(colInd) | reinterpret_cast<uintptr_t>(values)) % 16 == 0;
+        const int a0 = vector ? (j0 & ~3) : j0;
+        const int count = j1 - a0;
+        for (int e = 4 * tid; e < count; e += 4 * kThreads) {
+            int32_t c[4];
+            float w[4];
+            const int g = a0 + e;
+            if (vector && g + 4 <= nnz) {
+                const int4 cv = __ldcs(reinterpret_cast<const int4*>(colInd + g));
+                const float4 wv = __ldcs(reinterpret_cast<const float4*>(values + g));
+                c[0] = cv.x; c[1] = cv.y; c[2] = cv.z; c[3] = cv.w;
+                w[0] = wv.x; w[1] = wv.y; w[2] = wv.z; w[3] = wv.w;
+            } else {
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const bool in = g + q < nnz;
+                    c[q] = in ? __ldcs(colInd + g + q) : -1;
+                    w[q] = in ? __ldcs(values + g + q) : 0.0f;
+                }
+            }
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const int k = g + q - j0;
+                if (k >= 0 && k < nt) {
+                    const uint32_t col = static_cast<uint32_t>(c[q]) - p.indexBase;
+                    sCol[k] = col < p.cols ? static_cast<int>(col) : -1;
+                    sVal[k] = w[q];
+                }
+            }
+        }
+    }
+    __syncthreads();
+
+    // This warp's piece of the tile: local rows [r0, r1) end in it, local
+    // non-zeros [q0, q1) belong to it.
+    const int items = nr + nt;
+    int da = warp * kWarpItems;
+    int db = da + kWarpItems;
+    da = da < items ? da : items;
+    db = db < items ? db : items;
+    const int r0 = LocalMergeRow(sOff, nr, nt, da);
+    const int r1 = LocalMergeRow(sOff, nr, nt, db);
+    const int q0 = da - r0;
+    const int q1 = db - r1;
+    const bool headOpen = sOff[r0] < q0;  // row r0 began in an earlier warp or tile
+    if (lane == 0) {
+        sWarpRow[warp] = r0;
+        sHasHead[warp] = (headOpen && r1 > r0) ? 1 : 0;
+        if (warp == kWarps - 1) {
+            sWarpRow[kWarps] = r1;
+        }
+    }
+
+    const Scalars sc = LoadScalars(p);
+    float* ring = sRing + warp * kStages * kPanel + lane * VW;
+    const bool tileHeadOpen = sOff[0] < 0;
+
+    for (int col0 = 0; col0 < n; col0 += kPanel) {
+        const int colL = col0 + lane * VW;
+        const bool colOk = colL < n;  // n is a multiple of VW whenever VW > 1
+        const float* bLane = B + static_cast<int64_t>(colL) * ds.bCol;
+        float* cLane = C + static_cast<int64_t>(colL) * ds.cCol;
+
+        float acc[VW];
+#pragma unroll
+        for (int v = 0; v < VW; ++v) {
+            acc[v] = 0.0f;
+        }
+        auto issue = [&](int q) {
+            const int c = sCol[q];
+            if (c >= 0 && colOk) {
+                CpAsync<4 * VW>(ring + (q % kStages) * kPanel, bLane + static_cast<int64_t>(c) * ds.bRow);
+            }
+            CpAsyncCommit();
+        };
+        auto storeRow = [&](int localRow) {
+            if (!colOk) {
+                return;
+            }
+            float* dst = cLane + static_cast<int64_t>(i0 + localRow) * ds.cRow;
+            if (VW == 1) {
+                dst[0] = sc.betaZero ? sc.alpha * acc[0] : sc.alpha * acc[0] + sc.beta * dst[0];
+            } else {
+                V out;
+                float* o = reinterpret_cast<float*>(&out);
+                if (sc.betaZero) {
+#pragma unroll
+                    for (int v = 0; v < VW; ++v) {
+                        o[v] = sc.alpha * acc[v];
+                    }
+                } else {
+                    const V old = *reinterpret_cast<const V*>(dst);
+                    const float* od = reinterpret_cast<const float*>(&old);
+#pragma unroll
+                    for (int v = 0; v < VW; ++v) {
+                        o[v] = sc.alpha * acc[v] + sc.beta * od[v];
+                    }
+                }
+                *reinterpret_cast<V*>(dst) = out;
+            }
+        };
+        // A finished row goes to C, unless it is the warp's first row and its
+        // beginning lies elsewhere: then it waits in shared memory.
+        bool first = true;
+        auto flush = [&](int localRow) {
+            if (first && headOpen) {
+                if (colOk) {
+#pragma unroll
+                    for (int v = 0; v < VW; ++v) {
+                        sHead[warp * kPanel + lane * VW + v] = acc[v];
+                    }
+                }
+            } else {
+                storeRow(localRow);
+            }
+            first = false;
+#pragma unroll
+            for (int v = 0; v < VW; ++v) {
+                acc[v] = 0.0f;
+            }
+        };
+
+        int row = r0;
+        int rowEnd = row < nr ? sOff[row + 1] : nt + 1;  // the open tail row never ends here
+#pragma unroll
+        for (int s = 0; s < kStages; ++s) {
+            if (q0 + s < q1) {
+                issue(q0 + s);
+            } else {
+                CpAsyncCommit();
+            }
+        }
+        for (int q = q0; q < q1; ++q) {
+            while (rowEnd <= q && row < r1) {
+                flush(row);
+                ++row;
+                rowEnd = row < nr ? sOff[row + 1] : nt + 1;
+            }
+            CpAsyncWait<kStages - 1>();
+            const int c = sCol[q];
+            if (c >= 0 && colOk) {
+                const V b = *reinterpret_cast<const V*>(ring + (q % kStages) * kPanel);
+                const float a = sVal[q];
+                const float* bv = reinterpret_cast<const float*>(&b);
+#pragma unroll
+                for (int v = 0; v < VW; ++v) {
+                    acc[v] = fmaf(a, bv[v], acc[v]);
+                }
+            }
+            if (q + kStages < q1) {
+                issue(q + kStages);
+            } else {
+                CpAsyncCommit();
+            }
+        }
+        while (row < r1) {
+            flush(row);
+            ++row;
+        }
+        if (colOk) {  // what is left belongs to the row that continues past this warp
+#pragma unroll
+            for (int v = 0; v < VW; ++v) {
+                sTail[warp * kPanel + lane * VW + v] = acc[v];
+            }
+        }
+        CpAsyncWait<0>();
+        __syncthreads();
+
+        // Rows shared between warps: add the tails of the warps the row
+        // crossed, oldest first, then this warp's head piece.
+        if (sHasHead[warp] != 0 && colOk) {
+            int firstWarp = warp;
+            while (firstWarp > 0 && sWarpRow[firstWarp] == r0) {
+                --firstWarp;
+            }
+#pragma unroll
+            for (int v = 0; v < VW; ++v) {
+                float sum = 0.0f;
+                for (int u = firstWarp; u < warp; ++u) {
+                    sum += sTail[u * kPanel + lane * VW + v];
+                }
+                acc[v] = sum + sHead[warp * kPanel + lane * VW + v];
+            }
+            // The chain reaches back to the tile's first item exactly when the
+            // row is the tile's first row; then an earlier tile holds more of it.
+            if (r0 == 0 && tileHeadOpen) {
+#pragma unroll
+                for (int v = 0; v < VW; ++v) {
+                    tileHead[colL + v] = acc[v];
+                }
+            } else {
+                storeRow(r0);
+            }
+        }
+        if (warp == kWarps - 1 && colOk) {
+            int firstWarp = kWarps;
+            while (firstWarp > 0 && sWarpRow[firstWarp] == nr) {
+                --firstWarp;
+            }
+#pragma unroll
+            for (int v = 0; v < VW; ++v) {
+                float sum = 0.0f;
+                for (int u = firstWarp; u < kWarps; ++u) {
+                    sum += sTail[u * kPanel + lane * VW + v];
+                }
+                tileTail[colL + v] = sum;
+            }
+        }
+        __syncthreads();
+    }
+}
+
+// One warp per tile whose first row began in an earlier tile and ends in this
+// one: adds the tails of the tiles the row crossed, oldest first, then the head
+// piece, and writes the row of C.
+__global__ void SpmmCarryFixupKernel(float* __restrict__ C, SpmmPlanView plan, AclspSpmmParams p, DenseStrides ds)
+{
+    const int lane = threadIdx.x & 31;
+    const uint32_t warpsPerGrid = gridDim.x * (blockDim.x >> 5);
+    const int nnz = static_cast<int>(p.nnz);
+    const int n = static_cast<int>(p.n);
+    const int64_t total = static_cast<int64_t>(p.rows) + nnz;
+    const Scalars sc = LoadScalars(p);
+    for (uint32_t t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); t < plan.numTiles; t += warpsPerGrid) {
+        const int i0 = plan.tileRow[t];
+        const int i1 = plan.tileRow[t + 1];
+        if (i1 <= i0 || i0 < 0 || i0 >= static_cast<int>(p.rows)) {
+            continue;
+        }
+        int64_t d0 = static_cast<int64_t>(t) * kTile;
+        d0 = d0 < total ? d0 : total;
+        if (ClampOffset(plan.rowPtr[i0], nnz) >= d0 - i0) {
+            continue;
+        }
+        uint32_t first = t;
+        while (first > 0 && plan.tileRow[first] == i0) {
+            --first;
+        }
+        for (int c = lane; c < n; c += 32) {
+            double sum = 0.0;
+            for (uint32_t u = first; u < t; ++u) {
+                sum += static_cast<double>(plan.carry[static_cast<size_t>(2 * u) * n + c]);
+            }
+            sum += static_cast<double>(plan.carry[static_cast<size_t>(2 * t + 1) * n + c]);
+            float* dst = C + static_cast<int64_t>(i0) * ds.cRow + static_cast<int64_t>(c) * ds.cCol;
+            const float s = static_cast<float>(sum);
+            *dst = sc.betaZero ? sc.alpha * s : sc.alpha * s + sc.beta * *dst;
+        }
+    }
+}
+
+template <int VW>
+void Launch(const void* colInd, const void* values, const void* b, void* c, const SpmmPlanView& plan,
+            const AclspSpmmParams& p, const DenseStrides& ds, cudaStream_t s)
+{
+    constexpr size_t smem = SmemBytes(VW);
+    // More than 48 KiB of dynamic shared memory has to be requested per kernel
+    // and per device; the attribute is cheap to set, so it is set every time.
+    cudaFuncSetAttribute(SpmmTileKernel<VW>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    SpmmTileKernel<VW><<<plan.numTiles, kThreads, smem, s>>>(
+        static_cast<const int32_t*>(colInd), static_cast<const float*>(values), static_cast<const float*>(b),
+        static_cast<float*>(c), plan, p, ds);
+}
+
+}  // namespace
+
+extern "C" void spmm_b200_kernel_do(const void* colInd, const void* values, const void* b, void* c,
+                                    void* workspace, const AclspSpmmParams* params, void* stream)
+{
+    auto s = static_cast<cudaStream_t>(stream);
+    const AclspSpmmParams p = *params;
+    const SpmmPlanView plan = MakeView(workspace, p.rows, p.nnz, p.n);
+    if (plan.numTiles == 0 || p.n == 0) {
+        return;
+    }
+    // op(B)[r, c]: B is stored k x n when opB == 0 and n x k otherwise.
+    DenseStrides ds;
+    const bool bElementRowMajor = (p.opB == 0) == (p.orderB == 0);
+    ds.bRow = bElementRowMajor ? p.ldb : 1;
+    ds.bCol = bElementRowMajor ? 1 : p.ldb;
+    ds.cRow = p.orderC == 0 ? p.ldc : 1;
+    ds.cCol = p.orderC == 0 ? 1 : p.ldc;
+
+    const bool unit = ds.bCol == 1 && ds.cCol == 1;
+    const uintptr_t addr = reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(c);
+    int vw = 1;
+    if (unit && p.n % 4 == 0 && p.n >= 128 && p.ldb % 4 == 0 && p.ldc % 4 == 0 && addr % 16 == 0) {
+        vw = 4;
+    } else if (unit && p.n % 2 == 0 && p.n >= 64 && p.ldb % 2 == 0 && p.ldc % 2 == 0 && addr % 8 == 0) {
+        vw = 2;
+    }
+    if (vw == 4) {
+        Launch<4>(colInd, values, b, c, plan, p, ds, s);
+    } else if (vw == 2) {
+        Launch<2>(colInd, values, b, c, plan, p, ds, s);
+    } else {
+        Launch<1>(colInd, values, b, c, plan, p, ds, s);
+    }
+    uint32_t blocks = (plan.numTiles + 7u) / 8u;
+    blocks = blocks > 148u * 8u ? 148u * 8u : blocks;
+    SpmmCarryFixupKernel<<<blocks, 256, 0, s>>>(static_cast<float*>(c), plan, p, ds);
+}

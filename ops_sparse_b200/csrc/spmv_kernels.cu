@@ -1,0 +1,367 @@
+/*
+ * CSR SpMV for sm_100a:  y = alpha * A * x + beta * y,  fp32 data, int32 indices.
+ *
+ * Work decomposition.  The matrix is cut along the merge path of (row ends,
+ * non-zeros) into tiles of kTile items, so a tile holds at most kTile
+ * non-zeros plus rows whatever the row-length distribution: short rows, empty
+ * rows and 200 000-entry rows all cost the same per item.  One CTA owns one
+ * tile:
+ *   1. the tile's slice of colInd / values is streamed with 128-bit loads
+ *      (evict-first: it is read exactly once), x[col] is gathered through the
+ *      read-only path, and the exact fp64 products are staged in shared memory;
+ *   2. rows that end inside the tile are reduced by groups of 2^class lanes
+ *      ("vector per row", class picked per tile by the preprocessing pass from
+ *      the tile's mean row length; class 5 is warp per row) with a shuffle
+ *      tree; row pieces of kLongSegment products or more are reduced by the
+ *      whole CTA instead;
+ *   3. the piece of a row that continues into the next tile becomes the tile's
+ *      carry-out, and the piece of a row that began in an earlier tile becomes
+ *      its head partial; a second small kernel adds the carries of a split row
+ *      in tile order and writes that row.
+ * Every sum is taken in a fixed order, so results are bit-reproducible.
+ *
+ * Accuracy.  fp32 x fp32 products are exact in fp64 and all sums are fp64, so
+ * a row is as accurate as the reference's host golden (SpmvCpu with a double
+ * accumulator, test/spmv/arch22/spmv_test.cpp:258-279,309-348) up to the order
+ * of the additions; the reference's device kernels reach for compensated
+ * arithmetic for the same reason (sparse/spmv/arch22/kernels/spmv_kernel.h:19-68).
+ *
+ * The kernels never read or write out of bounds for any content of the index
+ * arrays: offsets are clamped to [0, nnz] and entries whose column falls
+ * outside [0, cols) are skipped, as the reference's kernels do
+ * (sparse/spmv/arch35/spmv_kernel.cpp:511-521).
+ */
+#include <cstdint>
+
+#include <cuda_runtime.h>
+
+#include "aclsparse_b200_kernels.h"
+#include "plan_layout.h"
+
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kWarps = kThreads / 32;
+constexpr int kTile = ACLSP_SPMV_TILE_ITEMS;
+constexpr int kLongSegment = 512;
+constexpr int kMaxLong = kTile / kLongSegment;
+
+struct SpmvPlanView {
+    const int32_t* rowPtr;  // base-0 row offsets, rows + 1 entries
+    int32_t* tileRow;       // numTiles + 1
+    int32_t* tileClass;     // numTiles
+    double* carry;          // 2 * numTiles: [2t] tail carry-out, [2t+1] head partial
+    uint32_t numTiles;
+};
+
+__host__ __device__ inline SpmvPlanView MakeView(void* workspace, uint32_t rows, uint32_t nnz)
+{
+    AclspPlanLayout l;
+    aclspSpmvLayout(rows, nnz, &l);
+    auto* base = static_cast<unsigned char*>(workspace);
+    SpmvPlanView v;
+    v.rowPtr = reinterpret_cast<const int32_t*>(base + l.rowPtrOff);
+    v.tileRow = reinterpret_cast<int32_t*>(base + l.tileRowOff);
+    v.tileClass = reinterpret_cast<int32_t*>(base + l.tileClassOff);
+    v.carry = reinterpret_cast<double*>(base + l.carryOff);
+    v.numTiles = l.numTiles;
+    return v;
+}
+
+__device__ __forceinline__ int ClampOffset(int v, int nnz)
+{
+    return v < 0 ? 0 : (v > nnz ? nnz : v);
+}
+
+/* ------------------------------------------------------------ product -- */
+
+struct Scalars {
+    double alpha;
+    double beta;
+    bool betaZero;
+};
+
+__device__ __forceinline__ Scalars LoadScalars(const AclspSpmvParams& p)
+{
+    const float a = p.alphaPtr != nullptr ? *p.alphaPtr : p.alpha;
+    const float b = p.betaPtr != nullptr ? *p.betaPtr : p.beta;
+    Scalars s;
+    s.alpha = static_cast<double>(a);
+    s.beta = static_cast<double>(b);
+    s.betaZero = b == 0.0f;
+    return s;
+}
+
+// beta == 0 must not read y: it may hold NaN or be uninitialised.
+__device__ __forceinline__ void StoreRow(float* __restrict__ y, int64_t index, double sum, const Scalars& s)
+{
+    const double r = s.betaZero ? s.alpha * sum : s.alpha * sum + s.beta * static_cast<double>(y[index]);
+    y[index] = static_cast<float>(r);
+}
+
+__device__ __forceinline__ double Product(float a, int32_t rawCol, const float* __restrict__ x, uint32_t base,
+                                          uint32_t cols, int64_t xStride)
+{
+    const uint32_t c = static_cast<uint32_t>(rawCol) - base;
+    if (c >= cols) {
+        return 0.0;
+    }
+    return static_cast<double>(a) * static_cast<double>(__ldg(x + static_cast<int64_t>(c) * xStride));
+}
+
+template <bool kVector>
+__global__ void __launch_bounds__(kThreads)
+SpmvTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ values, const float* __restrict__ x,
+               float* __restrict__ y, SpmvPlanView plan, AclspSpmvParams p)
+{
+    // Products first, the tile's row offsets packed against the end: a tile
+    // has nt products and nr + 1 offsets with nt + nr <= kTile.
+    __shared__ double sProd[kTile + 2];
+    __shared__ double sWarp[kWarps];
+    __shared__ int sLong[kMaxLong];
+    __shared__ int sNumLong;
+
+    const int tid = threadIdx.x;
+    const int t = blockIdx.x;
+    const int nnz = static_cast<int>(p.nnz);
+    const int64_t total = static_cast<int64_t>(p.rows) + nnz;
+    int64_t d0 = static_cast<int64_t>(t) * kTile;
+    int64_t d1 = d0 + kTile;
+    d0 = d0 < total ? d0 : total;
+    d1 = d1 < total ? d1 : total;
+    const int i0 = plan.tileRow[t];
+    const int i1 = plan.tileRow[t + 1];
+    const int j0 = static_cast<int>(d0 - i0);
+    const int j1 = static_cast<int>(d1 - i1);
+    const int nr = i1 - i0;
+    const int nt = j1 - j0;
+    // Row offsets that are not non-decreasing can produce an inconsistent
+    // split; such a tile is skipped rather than trusted.
+    if (nr < 0 || nt < 0 || nr + nt > kTile || i0 < 0 || i1 > static_cast<int>(p.rows) || j0 < 0 || j1 > nnz) {
+        if (tid == 0) {
+            plan.carry[2 * t] = 0.0;
+            plan.carry[2 * t + 1] = 0.0;
+        }
+        return;
+    }
+    int* sOff = reinterpret_cast<int*>(sProd + kTile + 2) - (nr + 2);
+    if (tid == 0) {
+        sNumLong = 0;
+    }
+    for (int k = tid; k <= nr; k += kThreads) {
+        sOff[k] = ClampOffset(plan.rowPtr[i0 + k], nnz) - j0;
+    }
+
+    if (kVector) {
+        // Vectors are aligned to 4 elements of the arrays, not of the tile.
+        const int a0 = j0 & ~3;
+        const int nvec = (j1 - a0 + 3) >> 2;
+        struct Vec4 {
+            int32_t c[4];
+            float w[4];
+        };
+        auto loadVec = [&](int v, Vec4& o) {
+            const int e = a0 + 4 * v;
+            if (e + 4 <= nnz) {
+                const int4 cv = __ldcs(reinterpret_cast<const int4*>(colInd + e));
+                const float4 wv = __ldcs(reinterpret_cast<const float4*>(values + e));
+                o.c[0] = cv.x; o.c[1] = cv.y; o.c[2] = cv.z; o.c[3] = cv.w;
+                o.w[0] = wv.x; o.w[1] = wv.y; o.w[2] = wv.z; o.w[3] = wv.w;
+            } else {  // the last vector of the arrays may be partial
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const bool in = e + q < nnz;
+                    o.c[q] = in ? __ldcs(colInd + e + q) : -1;
+                    o.w[q] = in ? __ldcs(values + e + q) : 0.0f;
+                }
+            }
+        };
+        auto useVec = [&](int v, const Vec4& o) {
+            const int k0 = a0 + 4 * v - j0;
+            double pr[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                pr[q] = Product(o.w[q], o.c[q], x, p.indexBase, p.cols, 1);
+            }
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const int k = k0 + q;
+                if (k >= 0 && k < nt) {
+                    sProd[k] = pr[q];
+                }
+            }
+        };
+        // A tile spans at most kTile / 4 + 1 vectors: two per thread, both
+        // loads in flight before either is used, plus a one-vector remainder.
+        Vec4 va, vb;
+        const bool hasA = tid < nvec;
+        const bool hasB = tid + kThreads < nvec;
+        if (hasA) {
+            loadVec(tid, va);
+        }
+        if (hasB) {
+            loadVec(tid + kThreads, vb);
+        }
+        if (hasA) {
+            useVec(tid, va);
+        }
+        if (hasB) {
+            useVec(tid + kThreads, vb);
+        }
+        for (int v = tid + 2 * kThreads; v < nvec; v += kThreads) {
+            Vec4 vc;
+            loadVec(v, vc);
+            useVec(v, vc);
+        }
+    } else {
+        for (int k = tid; k < nt; k += kThreads) {
+            const int64_t e = static_cast<int64_t>(j0) + k;
+            sProd[k] = Product(values[e * p.valuesStride], colInd[e * p.colIndStride], x, p.indexBase, p.cols,
+                               p.xStride);
+        }
+    }
+    __syncthreads();
+
+    const Scalars sc = LoadScalars(p);
+    const bool headOpen = sOff[0] < 0;  // row i0 began in an earlier tile
+    const int nseg = nr + 1;            // rows ending here, then the open tail
+
+    auto segBegin = [&](int k) { const int b = sOff[k]; return b < 0 ? 0 : (b > nt ? nt : b); };
+    auto segEnd = [&](int k) {
+        if (k >= nr) {
+            return nt;
+        }
+        const int e = sOff[k + 1];
+        return e < 0 ? 0 : (e > nt ? nt : e);
+    };
+    auto emit = [&](int k, double sum) {
+        if (k >= nr) {
+            plan.carry[2 * t] = sum;
+        } else if (k == 0 && headOpen) {
+            plan.carry[2 * t + 1] = sum;
+        } else {
+            StoreRow(y, static_cast<int64_t>(i0 + k) * p.yStride, sum, sc);
+        }
+    };
+
+    // Vector per row: 2^cls lanes share a row piece.
+    const int cls = plan.tileClass[t] & 7;
+    const int lanes = 1 << (cls > 5 ? 5 : cls);
+    const int lane = tid & (lanes - 1);
+    const int group = tid >> (cls > 5 ? 5 : cls);
+    const int ngroups = kThreads / lanes;
+    for (int k0 = 0; k0 < nseg; k0 += ngroups) {
+        const int k = k0 + group;
+        bool active = k < nseg;
+        double sum = 0.0;
+        if (active) {
+            const int b = segBegin(k);
+            const int e = segEnd(k);
+            if (e - b >= kLongSegment) {
+                if (lane == 0) {
+                    sLong[atomicAdd(&sNumLong, 1)] = k;
+                }
+                active = false;
+            } else {
+                for (int q = b + lane; q < e; q += lanes) {
+                    sum += sProd[q];
+                }
+            }
+        }
+        __syncwarp();
+        for (int o = lanes >> 1; o > 0; o >>= 1) {
+            sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        }
+        if (active && lane == 0) {
+            emit(k, sum);
+        }
+    }
+    __syncthreads();
+
+    // Long pieces: the whole CTA adds one piece, warps combined in warp order.
+    const int numLong = sNumLong;
+    for (int q = 0; q < numLong; ++q) {
+        const int k = sLong[q];
+        const int b = segBegin(k);
+        const int e = segEnd(k);
+        double sum = 0.0;
+        for (int i = b + tid; i < e; i += kThreads) {
+            sum += sProd[i];
+        }
+        for (int o = 16; o > 0; o >>= 1) {
+            sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        }
+        if ((tid & 31) == 0) {
+            sWarp[tid >> 5] = sum;
+        }
+        __syncthreads();
+        if (tid == 0) {
+            double totalSum = 0.0;
+#pragma unroll
+            for (int w = 0; w < kWarps; ++w) {
+                totalSum += sWarp[w];
+            }
+            emit(k, totalSum);
+        }
+        __syncthreads();
+    }
+}
+
+// One thread per tile whose first row began in an earlier tile and ends in
+// this one: adds the carry-outs of the tiles the row crossed, oldest first,
+// then the head partial, and writes the row.
+__global__ void SpmvCarryFixupKernel(float* __restrict__ y, SpmvPlanView plan, AclspSpmvParams p)
+{
+    const uint32_t t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= plan.numTiles) {
+        return;
+    }
+    const int nnz = static_cast<int>(p.nnz);
+    const int i0 = plan.tileRow[t];
+    const int i1 = plan.tileRow[t + 1];
+    if (i1 <= i0 || i0 < 0 || i0 >= static_cast<int>(p.rows)) {
+        return;
+    }
+    const int64_t total = static_cast<int64_t>(p.rows) + nnz;
+    int64_t d0 = static_cast<int64_t>(t) * kTile;
+    d0 = d0 < total ? d0 : total;
+    const int64_t j0 = d0 - i0;
+    if (ClampOffset(plan.rowPtr[i0], nnz) >= j0) {
+        return;
+    }
+    uint32_t first = t;
+    while (first > 0 && plan.tileRow[first] == i0) {
+        --first;
+    }
+    double sum = 0.0;
+    for (uint32_t u = first; u < t; ++u) {
+        sum += plan.carry[2 * u];
+    }
+    sum += plan.carry[2 * t + 1];
+    StoreRow(y, static_cast<int64_t>(i0) * p.yStride, sum, LoadScalars(p));
+}
+
+}  // namespace
+
+extern "C" void spmv_b200_kernel_do(const void* colInd, const void* values, const void* x, void* y,
+                                    void* workspace, const AclspSpmvParams* params, void* stream)
+{
+    auto s = static_cast<cudaStream_t>(stream);
+    const AclspSpmvParams p = *params;
+    const SpmvPlanView plan = MakeView(workspace, p.rows, p.nnz);
+    if (plan.numTiles == 0) {
+        return;
+    }
+    const bool vector = p.colIndStride == 1 && p.valuesStride == 1 && p.xStride == 1 &&
+                        reinterpret_cast<uintptr_t>(colInd) % 16 == 0 && reinterpret_cast<uintptr_t>(values) % 16 == 0;
+    if (vector) {
+        SpmvTileKernel<true><<<plan.numTiles, kThreads, 0, s>>>(
+            static_cast<const int32_t*>(colInd), static_cast<const float*>(values), static_cast<const float*>(x),
+            static_cast<float*>(y), plan, p);
+    } else {
+        SpmvTileKernel<false><<<plan.numTiles, kThreads, 0, s>>>(
+            static_cast<const int32_t*>(colInd), static_cast<const float*>(values), static_cast<const float*>(x),
+            static_cast<float*>(y), plan, p);
+    }
+    SpmvCarryFixupKernel<<<(plan.numTiles + 255u) / 256u, 256, 0, s>>>(static_cast<float*>(y), plan, p);
+}

@@ -1,0 +1,310 @@
+"""TEST INFRASTRUCTURE ONLY: Python face of the CPU oracle.
+
+Loads ``oracle/liboracle.so`` (the C restatement in ``oracle.c``) and, when it
+was built, ``oracle/_ref/libref_host.so`` (a few of the reference's own host
+sources compiled where they lie).  Only the tests, the smoke run and the
+benchmark's CPU-baseline leg import this module; the shipped library never does.
+
+Every function takes and returns numpy arrays.  The reference file:line each
+one follows is given in ``oracle.c`` next to the C function it calls.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import subprocess
+from ctypes import POINTER, c_double, c_float, c_int, c_int32, c_int64, c_uint32, c_uint64, c_void_p
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB_PATH = os.path.join(_HERE, "liboracle.so")
+_REF_PATH = os.path.join(_HERE, "_ref", "libref_host.so")
+
+RTOL = 1e-5  # tolerance of the fp32 outputs against the fp64 truth
+ATOL = 1e-6
+
+
+def build(ref: bool = True) -> None:
+    """Compile the oracle (and the reference-backed library when the reference checkout exists)."""
+    subprocess.run(["make", "-C", _HERE, "all"], check=True, capture_output=True)
+    if ref:
+        subprocess.run(["make", "-C", _HERE, "ref"], check=True, capture_output=True)
+
+
+def _load():
+    if not os.path.exists(_LIB_PATH):
+        build(ref=False)
+    return ctypes.CDLL(_LIB_PATH)
+
+
+_lib = _load()
+
+
+def _ptr(a: np.ndarray):
+    return a.ctypes.data_as(c_void_p)
+
+
+def _i32(a) -> np.ndarray:
+    return np.ascontiguousarray(a, dtype=np.int32)
+
+
+def _f32(a) -> np.ndarray:
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+_lib.oracle_spmv_f64.argtypes = [c_int64] + [c_void_p] * 6 + [c_float, c_float, c_int32, c_int]
+_lib.oracle_spmv_f32.argtypes = [c_int64] + [c_void_p] * 6 + [c_float, c_float, c_int32]
+_lib.oracle_spmv_transpose_f64.argtypes = [c_int64, c_int64] + [c_void_p] * 6 + [c_float, c_float, c_int32]
+_lib.oracle_spmm_f32.argtypes = [c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int,
+                                 c_void_p, c_int64, c_int, c_float, c_float, c_int32, c_int]
+_lib.oracle_spmm_f64.argtypes = [c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int,
+                                 c_int, c_void_p, c_int64, c_int, c_void_p, c_float, c_float, c_int32, c_int64,
+                                 c_int64, c_int]
+_lib.oracle_normalize_row_offsets.argtypes = [c_void_p, c_int64, c_int32, c_int64, c_void_p]
+_lib.oracle_ref_spmv_workspace_bytes.argtypes = [c_uint64]
+_lib.oracle_ref_spmv_workspace_bytes.restype = c_uint64
+_lib.oracle_ref_spmm_workspace_bytes.argtypes = [c_uint64, c_uint64]
+_lib.oracle_ref_spmm_workspace_bytes.restype = c_uint64
+_lib.oracle_greedy_row_bin_pack.argtypes = [c_void_p, c_int32, c_int32, c_void_p, c_void_p, POINTER(c_int32)]
+_lib.oracle_greedy_row_bin_pack.restype = c_int
+_lib.oracle_plan_tiles.argtypes = [c_void_p, c_int64, c_int64, c_uint32, c_uint32, c_void_p, c_void_p]
+_lib.oracle_row_block_bounds.argtypes = [c_void_p, c_int64, c_int64, c_int32, c_int32, c_void_p]
+_lib.oracle_check_tolerance.argtypes = [c_void_p, c_void_p, c_int64, c_double, c_double, POINTER(c_double),
+                                        POINTER(c_double)]
+_lib.oracle_check_tolerance.restype = c_int64
+_lib.oracle_max_threads.restype = c_int
+
+
+def max_threads() -> int:
+    return int(_lib.oracle_max_threads())
+
+
+# ------------------------------------------------------------------ SpMV --
+
+def spmv_f64(row_ptr, col_ind, values, x, y, alpha=1.0, beta=0.0, index_base=0, threads=1) -> np.ndarray:
+    """fp64-accumulated truth of alpha*A*x + beta*y (what the reference's tests compare fp32 SpMV against)."""
+    row_ptr, col_ind, values, x, y = _i32(row_ptr), _i32(col_ind), _f32(values), _f32(x), _f32(y)
+    rows = row_ptr.size - 1
+    out = np.empty(rows, dtype=np.float64)
+    _lib.oracle_spmv_f64(rows, _ptr(row_ptr), _ptr(col_ind), _ptr(values), _ptr(x), _ptr(y), _ptr(out),
+                         alpha, beta, index_base, threads)
+    return out
+
+
+def spmv_f32(row_ptr, col_ind, values, x, y, alpha=1.0, beta=0.0, index_base=0) -> np.ndarray:
+    row_ptr, col_ind, values, x, y = _i32(row_ptr), _i32(col_ind), _f32(values), _f32(x), _f32(y)
+    rows = row_ptr.size - 1
+    out = np.empty(rows, dtype=np.float32)
+    _lib.oracle_spmv_f32(rows, _ptr(row_ptr), _ptr(col_ind), _ptr(values), _ptr(x), _ptr(y), _ptr(out),
+                         alpha, beta, index_base)
+    return out
+
+
+def spmv_transpose_f64(row_ptr, col_ind, values, x, y, cols, alpha=1.0, beta=0.0, index_base=0) -> np.ndarray:
+    row_ptr, col_ind, values, x, y = _i32(row_ptr), _i32(col_ind), _f32(values), _f32(x), _f32(y)
+    out = np.empty(cols, dtype=np.float64)
+    _lib.oracle_spmv_transpose_f64(row_ptr.size - 1, cols, _ptr(row_ptr), _ptr(col_ind), _ptr(values), _ptr(x),
+                                   _ptr(y), _ptr(out), alpha, beta, index_base)
+    return out
+
+
+# ------------------------------------------------------------------ SpMM --
+
+def spmm_f32(row_ptr, col_ind, values, b, ldb, c, ldc, n, alpha=1.0, beta=0.0, b_row_major=True,
+             op_b_transpose=False, c_row_major=True, index_base=0, threads=1) -> np.ndarray:
+    """fp32 golden; ``b`` and ``c`` are flat storage arrays, the updated copy of ``c`` is returned."""
+    row_ptr, col_ind, values, b = _i32(row_ptr), _i32(col_ind), _f32(values), _f32(b)
+    out = np.array(c, dtype=np.float32, copy=True).ravel()
+    _lib.oracle_spmm_f32(row_ptr.size - 1, n, _ptr(row_ptr), _ptr(col_ind), _ptr(values), _ptr(b), ldb,
+                         int(b_row_major), int(op_b_transpose), _ptr(out), ldc, int(c_row_major), alpha, beta,
+                         index_base, threads)
+    return out
+
+
+def spmm_f64(row_ptr, col_ind, values, b, ldb, c, ldc, n, k, alpha=1.0, beta=0.0, b_row_major=True,
+             op_b_transpose=False, c_row_major=True, index_base=0, row_begin=0, row_end=None,
+             threads=1) -> np.ndarray:
+    """fp64 truth of rows [row_begin, row_end), returned row-major with n columns."""
+    row_ptr, col_ind, values, b = _i32(row_ptr), _i32(col_ind), _f32(values), _f32(b)
+    c = _f32(c).ravel()
+    m = row_ptr.size - 1
+    row_end = m if row_end is None else row_end
+    out = np.empty((row_end - row_begin, n), dtype=np.float64)
+    _lib.oracle_spmm_f64(m, n, k, _ptr(row_ptr), _ptr(col_ind), _ptr(values), _ptr(b), ldb, int(b_row_major),
+                         int(op_b_transpose), _ptr(c), ldc, int(c_row_major), _ptr(out), alpha, beta, index_base,
+                         row_begin, row_end, threads)
+    return out
+
+
+# -------------------------------------------------------------- metadata --
+
+def normalize_row_offsets(row_ptr, rows, index_base=0, stride=1) -> np.ndarray:
+    row_ptr = _i32(row_ptr)
+    out = np.empty(rows + 1, dtype=np.int32)
+    _lib.oracle_normalize_row_offsets(_ptr(row_ptr), rows, index_base, stride, _ptr(out))
+    return out
+
+
+def ref_spmv_workspace_bytes(rows: int) -> int:
+    return int(_lib.oracle_ref_spmv_workspace_bytes(rows))
+
+
+def ref_spmm_workspace_bytes(m: int, bins: int) -> int:
+    return int(_lib.oracle_ref_spmm_workspace_bytes(m, bins))
+
+
+def greedy_row_bin_pack(row_nnz, bins: int):
+    """Returns (reorder, bin_edges, identity_reorder, uniform_degree) of the reference's SpMM preprocessing."""
+    row_nnz = _i32(row_nnz)
+    reorder = np.empty(row_nnz.size, dtype=np.int32)
+    edges = np.empty(bins + 1, dtype=np.int32)
+    uniform = c_int32(0)
+    identity = _lib.oracle_greedy_row_bin_pack(_ptr(row_nnz), row_nnz.size, bins, _ptr(reorder), _ptr(edges),
+                                               ctypes.byref(uniform))
+    return reorder, edges, bool(identity), int(uniform.value)
+
+
+SPMV_TILE_ITEMS = 2048
+SPMM_TILE_ITEMS = 1024
+HEADER_BYTES = 192
+PLAN_MAGIC = 0x30303242
+
+
+def _align64(v: int) -> int:
+    return (v + 63) & ~63
+
+
+def plan_layout(rows: int, nnz: int, tile_items: int, carry_bytes_per_tile: int) -> dict:
+    """Offsets of the B200 plan inside the external buffer (twin of plan_layout.h)."""
+    num_tiles = (rows + nnz + tile_items - 1) // tile_items
+    row_ptr_off = HEADER_BYTES
+    tile_row_off = _align64(row_ptr_off + 4 * (rows + 1))
+    tile_class_off = _align64(tile_row_off + 4 * (num_tiles + 1))
+    carry_off = _align64(tile_class_off + 4 * num_tiles)
+    total = _align64(carry_off + carry_bytes_per_tile * num_tiles)
+    return dict(num_tiles=num_tiles, row_ptr_off=row_ptr_off, tile_row_off=tile_row_off,
+                tile_class_off=tile_class_off, carry_off=carry_off, total_bytes=total)
+
+
+def spmv_plan_layout(rows: int, nnz: int) -> dict:
+    return plan_layout(rows, nnz, SPMV_TILE_ITEMS, 16)
+
+
+def spmm_plan_layout(rows: int, nnz: int, dense_cols: int) -> dict:
+    return plan_layout(rows, nnz, SPMM_TILE_ITEMS, 8 * dense_cols)
+
+
+def plan_tiles(row_ptr_n, nnz: int, tile_items: int, class_div: int):
+    """Merge-path tile splits and per-tile row bins (twin of the device preprocessing pass)."""
+    row_ptr_n = _i32(row_ptr_n)
+    rows = row_ptr_n.size - 1
+    num_tiles = (rows + nnz + tile_items - 1) // tile_items
+    tile_row = np.empty(num_tiles + 1, dtype=np.int32)
+    tile_class = np.empty(num_tiles, dtype=np.int32)
+    _lib.oracle_plan_tiles(_ptr(row_ptr_n), rows, nnz, tile_items, class_div, _ptr(tile_row), _ptr(tile_class))
+    return tile_row, tile_class
+
+
+def plan_header(kind: int, rows: int, cols: int, nnz: int, index_base: int, dense_cols: int, layout: dict,
+                tile_items: int) -> np.ndarray:
+    """The 80 meaningful bytes of the plan header, as the device writes them."""
+    head = np.zeros(10, dtype=np.uint32)
+    head[:] = [PLAN_MAGIC, 1, kind, tile_items, rows, cols, nnz, index_base, layout["num_tiles"], dense_cols]
+    tail = np.array([layout["row_ptr_off"], layout["tile_row_off"], layout["tile_class_off"], layout["carry_off"],
+                     layout["total_bytes"]], dtype=np.uint64)
+    return np.concatenate([head.view(np.uint8), tail.view(np.uint8)])
+
+
+def row_block_bounds(row_ptr, nnz: int, parts: int, index_base=0) -> np.ndarray:
+    row_ptr = _i32(row_ptr)
+    bounds = np.empty(parts + 1, dtype=np.int32)
+    _lib.oracle_row_block_bounds(_ptr(row_ptr), row_ptr.size - 1, nnz, index_base, parts, _ptr(bounds))
+    return bounds
+
+
+# -------------------------------------------------------------- verifier --
+
+def check_tolerance(got, truth, rtol=RTOL, atol=ATOL):
+    """Returns (violations, max_abs_err, max_rel_err) of |got - truth| <= atol + rtol*|truth| per element."""
+    got = _f32(got).ravel()
+    truth = np.ascontiguousarray(truth, dtype=np.float64).ravel()
+    assert got.size == truth.size
+    max_abs, max_rel = c_double(0.0), c_double(0.0)
+    bad = _lib.oracle_check_tolerance(_ptr(got), _ptr(truth), got.size, rtol, atol, ctypes.byref(max_abs),
+                                      ctypes.byref(max_rel))
+    return int(bad), float(max_abs.value), float(max_rel.value)
+
+
+# ------------------------------------------- the reference's own code --
+
+def have_ref() -> bool:
+    return os.path.exists(_REF_PATH)
+
+
+_ref = None
+
+
+def ref():
+    """The reference-backed library (only exists where the reference checkout was available at build time)."""
+    global _ref
+    if _ref is None:
+        _ref = ctypes.CDLL(_REF_PATH)
+        _ref.ref_spmm_golden_f64.argtypes = [c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_int64,
+                                             c_void_p, c_void_p, c_double, c_double, c_int, c_int32, c_void_p]
+        _ref.ref_fill_csr.argtypes = [c_int64, c_int64, c_double, c_double, c_double, c_double, c_uint32, c_void_p,
+                                      c_void_p, c_void_p, c_int64]
+        _ref.ref_fill_csr.restype = c_int64
+        _ref.ref_fill_dense.argtypes = [c_int64, c_double, c_double, c_uint32, c_void_p]
+        _ref.ref_spmv_workspace_bytes.argtypes = [c_uint64, c_uint64, c_int]
+        _ref.ref_spmv_workspace_bytes.restype = c_uint64
+        _ref.ref_spmm_row_reorder.argtypes = [c_void_p, c_int64, c_int64, c_int64, c_int32, c_void_p, c_void_p,
+                                              POINTER(c_int), POINTER(c_int32)]
+        _ref.ref_spmm_row_reorder.restype = c_uint32
+    return _ref
+
+
+def ref_spmm_golden_f64(row_ptr, col_ind, values, b, c_init, m, n, k, alpha, beta, op_b_transpose=False,
+                        index_base=0) -> np.ndarray:
+    row_ptr, col_ind, values = _i32(row_ptr), _i32(col_ind), _f32(values)
+    b, c_init = _f32(b).ravel(), _f32(c_init).ravel()
+    out = np.empty((m, n), dtype=np.float64)
+    ref().ref_spmm_golden_f64(m, n, k, _ptr(row_ptr), _ptr(col_ind), _ptr(values), values.size, _ptr(b),
+                              _ptr(c_init), alpha, beta, int(op_b_transpose), index_base, _ptr(out))
+    return out
+
+
+def ref_fill_csr(rows, cols, sparsity, seed, empty_row_prob=0.0, lo=-2.0, hi=2.0):
+    cap = max(16, int(rows * cols * (1.0 - sparsity) * 1.5) + 4 * int(rows) + 64)
+    while True:
+        rp = np.empty(rows + 1, dtype=np.int32)
+        ci = np.empty(cap, dtype=np.int32)
+        va = np.empty(cap, dtype=np.float32)
+        nnz = ref().ref_fill_csr(rows, cols, sparsity, empty_row_prob, lo, hi, seed, _ptr(rp), _ptr(ci), _ptr(va),
+                                 cap)
+        if nnz <= cap:
+            return rp, ci[:nnz].copy(), va[:nnz].copy()
+        cap = int(nnz)
+
+
+def ref_fill_dense(size, seed, lo=-2.0, hi=2.0) -> np.ndarray:
+    out = np.empty(size, dtype=np.float32)
+    ref().ref_fill_dense(size, lo, hi, seed, _ptr(out))
+    return out
+
+
+def ref_spmv_workspace_bytes_real(rows: int, cols: int, transpose=False) -> int:
+    return int(ref().ref_spmv_workspace_bytes(rows, cols, int(transpose)))
+
+
+def ref_spmm_row_reorder(row_ptr, k: int, bins: int):
+    row_ptr = _i32(row_ptr)
+    m = row_ptr.size - 1
+    nnz = int(row_ptr[-1] - row_ptr[0])
+    reorder = np.empty(m, dtype=np.int32)
+    edges = np.empty(bins + 1, dtype=np.int32)
+    identity, uniform = c_int(0), c_int32(0)
+    st = ref().ref_spmm_row_reorder(_ptr(row_ptr), m, k, nnz, bins, _ptr(reorder), _ptr(edges),
+                                    ctypes.byref(identity), ctypes.byref(uniform))
+    assert st == 0, st
+    return reorder, edges, bool(identity.value), int(uniform.value)
