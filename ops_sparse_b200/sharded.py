@@ -1,0 +1,156 @@
+"""Row-block sharding of CSR SpMV / SpMM over the GPUs of one node.
+
+One process per GPU (``torch.distributed``, NCCL over NVLink).  The matrix is cut
+into ``world_size`` contiguous row blocks that balance the non-zeros:
+
+    bounds[g] = min{ r : rowOffsets[r] - base >= ceil(g * nnz / G) },   bounds[G] = rows
+
+Rank g holds rows [bounds[g], bounds[g+1]) of A (row offsets rebased to start at
+0, its slice of the column indices and values), a full replica of x or B, and
+computes its slice of y or C with the single-GPU operators.  The only exchange
+is the all-gather that reassembles y / C on every rank; row blocks have unequal
+row counts, so slices travel padded to the largest block and are compacted by
+one concatenation afterwards.  The reference library is single-device; this
+layer has no counterpart there.
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from . import _lib as L
+
+
+def row_block_bounds_host(row_ptr: np.ndarray, nnz: int, parts: int, index_base: int = 0) -> np.ndarray:
+    """Host evaluation of the bounds formula above (the device version is aclsparseB200RowBlockBounds)."""
+    offs = np.asarray(row_ptr, dtype=np.int64)[:-1] - index_base
+    targets = (np.arange(parts + 1, dtype=np.int64) * nnz + parts - 1) // parts
+    bounds = np.searchsorted(offs, targets, side="left").astype(np.int32)
+    bounds[parts] = offs.size
+    return bounds
+
+
+def shard_csr(row_ptr: np.ndarray, col_ind: np.ndarray, values: np.ndarray, bounds: np.ndarray, rank: int,
+              index_base: int = 0):
+    """Rank's row block as a self-contained CSR: rebased row offsets and the matching index / value slices."""
+    r0, r1 = int(bounds[rank]), int(bounds[rank + 1])
+    p0, p1 = int(row_ptr[r0]) - index_base, int(row_ptr[r1]) - index_base
+    local_ptr = (np.asarray(row_ptr[r0:r1 + 1], dtype=np.int64) - row_ptr[r0] + index_base).astype(np.int32)
+    return local_ptr, col_ind[p0:p1], values[p0:p1]
+
+
+class _Gather:
+    """All-gather of unequal row blocks: padded slots, then one concatenation."""
+
+    def __init__(self, bounds: np.ndarray, rank: int, width: int, device, group=None):
+        self.rows = np.diff(bounds).astype(np.int64)
+        self.rank, self.width, self.group = rank, width, group
+        self.world = self.rows.size
+        self.max_rows = int(self.rows.max()) if self.rows.size else 0
+        shape = (self.world, max(self.max_rows, 1), width) if width > 1 else (self.world, max(self.max_rows, 1))
+        self.slots = torch.zeros(shape, dtype=torch.float32, device=device)
+        self.local = self.slots[rank][: int(self.rows[rank])]
+
+    def run(self) -> torch.Tensor:
+        if self.world > 1:
+            dist.all_gather_into_tensor(self.slots.view(-1), self.slots[self.rank].reshape(-1), group=self.group)
+        return torch.cat([self.slots[g][: int(self.rows[g])] for g in range(self.world)])
+
+
+class ShardedSpMV:
+    """y = alpha * A * x + beta * y with A row-block sharded over the ranks of ``group``.
+
+    ``local_product(local_csr, x, y_local, alpha, beta)`` computes one rank's slice; by default it is
+    the single-GPU C API.  (The multi-process CPU tests inject a stand-in here to exercise the
+    partition / gather logic without a GPU; there is no CPU implementation in this package.)
+    """
+
+    def __init__(self, cfg: dict, rank: int, world: int, device, group=None, local_product=None):
+        self.rank, self.world, self.device = rank, world, device
+        base = cfg.get("index_base", 0)
+        self.bounds = row_block_bounds_host(cfg["row_ptr"], cfg["nnz"], world, base)
+        self.local_ptr, self.local_col, self.local_val = shard_csr(cfg["row_ptr"], cfg["col_ind"], cfg["values"],
+                                                                   self.bounds, rank, base)
+        self.r0, self.r1 = int(self.bounds[rank]), int(self.bounds[rank + 1])
+        self.gather = _Gather(self.bounds, rank, 1, device, group)
+        self.x = torch.from_numpy(cfg["x"]).to(device)
+        self.y_local = self.gather.local
+        self.y_local.copy_(torch.from_numpy(cfg["y"][self.r0:self.r1]).to(device))
+        self._product = local_product
+        if local_product is None:
+            from . import api
+            self.d_ptr = torch.from_numpy(self.local_ptr).to(device)
+            self.d_col = torch.from_numpy(np.ascontiguousarray(self.local_col)).to(device)
+            self.d_val = torch.from_numpy(np.ascontiguousarray(self.local_val)).to(device)
+            self.handle = api.Handle()
+            self.mat = api.CsrMatrix(self.r1 - self.r0, cfg["cols"], self.d_ptr, self.d_col, self.d_val, base,
+                                     nnz=int(self.local_col.size))
+            self.op = api.SpMV(self.handle, self.mat, api.DnVec(self.x), api.DnVec(self.y_local,
+                                                                                   size=self.r1 - self.r0))
+            if self.r1 > self.r0:
+                self.op.preprocess()
+
+    def step(self, alpha: float, beta: float) -> torch.Tensor:
+        """One product: local slice, then the all-gather; returns the full y (identical on every rank)."""
+        if self._product is not None:
+            self._product((self.local_ptr, self.local_col, self.local_val), self.x, self.y_local, alpha, beta)
+        elif self.r1 > self.r0:
+            self.op(alpha, beta)
+        return self.gather.run()
+
+
+class ShardedSpMM:
+    """C = alpha * A * B + beta * C (row-major B and C) with A row-block sharded over the ranks."""
+
+    def __init__(self, cfg: dict, rank: int, world: int, device, group=None, local_product=None):
+        self.rank, self.world, self.device = rank, world, device
+        base = cfg.get("index_base", 0)
+        n = cfg["n"]
+        self.bounds = row_block_bounds_host(cfg["row_ptr"], cfg["nnz"], world, base)
+        self.local_ptr, self.local_col, self.local_val = shard_csr(cfg["row_ptr"], cfg["col_ind"], cfg["values"],
+                                                                   self.bounds, rank, base)
+        self.r0, self.r1 = int(self.bounds[rank]), int(self.bounds[rank + 1])
+        self.gather = _Gather(self.bounds, rank, n, device, group)
+        self.b = torch.from_numpy(cfg["b"]).to(device)
+        self.c_local = self.gather.local
+        self.c_local.copy_(torch.from_numpy(cfg["c"][self.r0:self.r1]).to(device))
+        self._product = local_product
+        if local_product is None:
+            from . import api
+            self.d_ptr = torch.from_numpy(self.local_ptr).to(device)
+            self.d_col = torch.from_numpy(np.ascontiguousarray(self.local_col)).to(device)
+            self.d_val = torch.from_numpy(np.ascontiguousarray(self.local_val)).to(device)
+            self.handle = api.Handle()
+            rows = self.r1 - self.r0
+            self.mat = api.CsrMatrix(rows, cfg["cols"], self.d_ptr, self.d_col, self.d_val, base,
+                                     nnz=int(self.local_col.size))
+            if rows > 0:
+                self.op = api.SpMM(self.handle, self.mat, api.DnMat(cfg["cols"], n, n, self.b),
+                                   api.DnMat(rows, n, n, self.c_local))
+                self.op.preprocess()
+
+    def step(self, alpha: float, beta: float) -> torch.Tensor:
+        if self._product is not None:
+            self._product((self.local_ptr, self.local_col, self.local_val), self.b, self.c_local, alpha, beta)
+        elif self.r1 > self.r0:
+            self.op(alpha, beta)
+        return self.gather.run()
+
+
+def init_process_group_from_env(backend: "str | None" = None):
+    """RANK / LOCAL_RANK / WORLD_SIZE / MASTER_* from the environment (torchrun); returns (rank, world, device)."""
+    import os
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    cuda = torch.cuda.is_available()
+    device = torch.device(f"cuda:{local}") if cuda else torch.device("cpu")
+    if cuda:
+        torch.cuda.set_device(device)
+    if world > 1 and not dist.is_initialized():
+        dist.init_process_group(backend or ("nccl" if cuda else "gloo"), rank=rank, world_size=world)
+    return rank, world, device
+
+
+__all__ = ["row_block_bounds_host", "shard_csr", "ShardedSpMV", "ShardedSpMM", "init_process_group_from_env", "L"]
