@@ -48,6 +48,8 @@ typedef struct AclspSpmmParams {
     uint32_t opB;            /* 0: B is k x n, 1: B is n x k and read transposed */
     uint32_t orderB;         /* 0 row-major, 1 column-major */
     uint32_t orderC;
+    uint32_t highPrecision;  /* 1: compensated fp32 accumulation (the FP32_HIGH_PRECISION algorithm) */
+    uint32_t reserved;
     int64_t ldb;
     int64_t ldc;
     float alpha;

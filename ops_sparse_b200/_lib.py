@@ -64,7 +64,7 @@ class SpmmParams(ctypes.Structure):
     """AclspSpmmParams of include/aclsparse_b200_kernels.h."""
     _fields_ = [("rows", c_uint32), ("cols", c_uint32), ("nnz", c_uint32), ("indexBase", c_uint32),
                 ("n", c_uint32), ("opB", c_uint32), ("orderB", c_uint32), ("orderC", c_uint32),
-                ("ldb", c_int64), ("ldc", c_int64), ("alpha", c_float), ("beta", c_float),
+                ("highPrecision", c_uint32), ("reserved", c_uint32), ("ldb", c_int64), ("ldc", c_int64), ("alpha", c_float), ("beta", c_float),
                 ("alphaPtr", c_void_p), ("betaPtr", c_void_p)]
 
 

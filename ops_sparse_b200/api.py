@@ -52,7 +52,9 @@ class Handle:
         return self._h
 
     def set_stream(self, cuda_stream: int) -> None:
-        check("aclsparseSetStream", L.lib().aclsparseSetStream(self._h, c_void_p(cuda_stream)))
+        # SpMV insists on a non-NULL stream, as the reference does.  PyTorch's default stream is the
+        # NULL stream; cudaStreamLegacy (0x1) is the explicit, non-NULL handle of that same stream.
+        check("aclsparseSetStream", L.lib().aclsparseSetStream(self._h, c_void_p(cuda_stream or 0x1)))
 
     def set_pointer_mode(self, mode: int) -> None:
         check("aclsparseSetPointerMode", L.lib().aclsparseSetPointerMode(self._h, mode))
@@ -180,8 +182,7 @@ class SpMV:
 
     def allocate(self, alpha=1.0, beta=0.0):
         n = self.buffer_size(alpha, beta)
-        self.buffer = torch.empty(max(n, 64), dtype=torch.uint8, device=self.mat.values.device
-                                  if self.mat.values is not None else "cuda")
+        self.buffer = torch.empty(max(n, 64), dtype=torch.uint8, device=self.y.values.device)
         return self.buffer
 
     def preprocess(self, alpha=1.0, beta=0.0) -> None:
@@ -219,7 +220,7 @@ class SpMM:
 
     def allocate(self, alpha=1.0, beta=0.0):
         n = self.buffer_size(alpha, beta)
-        self.buffer = torch.empty(max(n, 64), dtype=torch.uint8, device=self.mat.values.device)
+        self.buffer = torch.empty(max(n, 64), dtype=torch.uint8, device=self.c.values.device)
         return self.buffer
 
     def preprocess(self, alpha=1.0, beta=0.0) -> None:

@@ -84,7 +84,7 @@ static inline ACLSP_HD uint32_t aclspNumTiles(uint64_t rows, uint64_t nnz, uint3
 }
 
 /* carryBytesPerTile: SpMV keeps two doubles per tile (tail carry-out, head
- * partial); SpMM keeps two rows of denseCols floats. */
+ * partial); SpMM keeps two rows of denseCols doubles. */
 static inline ACLSP_HD void aclspPlanLayout(uint64_t rows, uint64_t nnz, uint32_t tileItems,
                                    uint64_t carryBytesPerTile, AclspPlanLayout* out)
 {
@@ -104,7 +104,7 @@ static inline ACLSP_HD void aclspSpmvLayout(uint64_t rows, uint64_t nnz, AclspPl
 
 static inline ACLSP_HD void aclspSpmmLayout(uint64_t rows, uint64_t nnz, uint64_t denseCols, AclspPlanLayout* out)
 {
-    aclspPlanLayout(rows, nnz, ACLSP_SPMM_TILE_ITEMS, 8u * denseCols, out);
+    aclspPlanLayout(rows, nnz, ACLSP_SPMM_TILE_ITEMS, 16u * denseCols, out);
 }
 
 /* Row bin of a tile with `nr` completed rows and `nt` non-zeros: the number

@@ -14,7 +14,10 @@
  *    the structure of A and the width of C only: calling with another B, C,
  *    alpha or beta reuses it (the reference rebuilds, spmm_host.cpp:63-97,199-215);
  *  - every algorithm value selects the same kernels, which add in a fixed
- *    order (so all of them are deterministic, as the reference's CSR_ALG3 is).
+ *    order (so all of them are deterministic, as the reference's CSR_ALG3 is);
+ *    FP32_HIGH_PRECISION additionally compensates the fp32 accumulation, as the
+ *    reference's Kahan variant does (spmm_kernel_simt.cpp:424-431), here together
+ *    with the rounding error of every product.
  */
 #include <cstdint>
 #include <limits>
@@ -280,6 +283,7 @@ extern "C" aclsparseStatus_t aclsparseSpMM(aclsparseHandle_t handle, aclsparseOp
     params.opB = opB == ACL_SPARSE_OP_NON_TRANSPOSE ? 0u : 1u;  // real data: H is T
     params.orderB = static_cast<uint32_t>(matB->order);
     params.orderC = static_cast<uint32_t>(matC->order);
+    params.highPrecision = alg == ACL_SPARSE_SPMM_CSR_FP32_HIGH_PRECISION_ALG ? 1u : 0u;
     params.ldb = matB->ld;
     params.ldc = matC->ld;
     if (handle->pointerMode == ACL_SPARSE_POINTER_MODE_DEVICE) {

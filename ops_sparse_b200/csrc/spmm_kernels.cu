@@ -52,7 +52,7 @@ constexpr int kStages = 8;
 struct SpmmPlanView {
     const int32_t* rowPtr;
     int32_t* tileRow;
-    float* carry;  // [numTiles][2][n]: tail carry-out, head partial
+    double* carry;  // [numTiles][2][n]: tail carry-out, head partial
     uint32_t numTiles;
 };
 
@@ -64,7 +64,7 @@ inline SpmmPlanView MakeView(void* workspace, uint32_t rows, uint32_t nnz, uint3
     SpmmPlanView v;
     v.rowPtr = reinterpret_cast<const int32_t*>(base + l.rowPtrOff);
     v.tileRow = reinterpret_cast<int32_t*>(base + l.tileRowOff);
-    v.carry = reinterpret_cast<float*>(base + l.carryOff);
+    v.carry = reinterpret_cast<double*>(base + l.carryOff);
     v.numTiles = l.numTiles;
     return v;
 }
@@ -153,11 +153,11 @@ constexpr size_t SmemBytes(int vw)
            + sizeof(int) * kTile                        // sCol
            + sizeof(float) * kTile                      // sVal
            + sizeof(float) * kWarps * kStages * 32 * vw // ring
-           + sizeof(float) * 2 * kWarps * 32 * vw       // warp tail / head
+           + sizeof(double) * 2 * kWarps * 32 * vw      // warp tail / head
            + sizeof(int) * (2 * kWarps + 2);            // warp row split, head flags
 }
 
-template <int VW>
+template <int VW, bool kCompensated>
 __global__ void __launch_bounds__(kThreads)
 SpmmTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ values, const float* __restrict__ B,
                float* __restrict__ C, SpmmPlanView plan, AclspSpmmParams p, DenseStrides ds)
@@ -166,10 +166,10 @@ SpmmTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ val
     constexpr int kPanel = 32 * VW;
 
     extern __shared__ __align__(16) unsigned char smemRaw[];
-    float* sRing = reinterpret_cast<float*>(smemRaw);                 // [kWarps][kStages][kPanel]
-    float* sTail = sRing + kWarps * kStages * kPanel;                 // [kWarps][kPanel]
-    float* sHead = sTail + kWarps * kPanel;                           // [kWarps][kPanel]
-    float* sVal = sHead + kWarps * kPanel;                            // [kTile]
+    double* sTail = reinterpret_cast<double*>(smemRaw);               // [kWarps][kPanel]
+    double* sHead = sTail + kWarps * kPanel;                          // [kWarps][kPanel]
+    float* sRing = reinterpret_cast<float*>(sHead + kWarps * kPanel); // [kWarps][kStages][kPanel]
+    float* sVal = sRing + kWarps * kStages * kPanel;                  // [kTile]
     int* sCol = reinterpret_cast<int*>(sVal + kTile);                 // [kTile], -1 marks a skipped entry
     int* sOff = sCol + kTile;                                         // [kTile + 2]
     int* sWarpRow = sOff + kTile + 2;                                 // [kWarps + 1] first local row of each warp
@@ -192,11 +192,11 @@ SpmmTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ val
     const int j1 = static_cast<int>(d1 - i1);
     const int nr = i1 - i0;
     const int nt = j1 - j0;
-    float* tileTail = plan.carry + static_cast<size_t>(2 * t) * n;
-    float* tileHead = tileTail + n;
+    double* tileTail = plan.carry + static_cast<size_t>(2 * t) * n;
+    double* tileHead = tileTail + n;
     if (nr < 0 || nt < 0 || nr + nt > kTile || i0 < 0 || i1 > static_cast<int>(p.rows) || j0 < 0 || j1 > nnz) {
         for (int c = tid; c < 2 * n; c += kThreads) {  // inconsistent row offsets: contribute nothing
-            tileTail[c] = 0.0f;
+            tileTail[c] = 0.0;
         }
         return;
     }
@@ -269,10 +269,15 @@ SpmmTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ val
         const float* bLane = B + static_cast<int64_t>(colL) * ds.bCol;
         float* cLane = C + static_cast<int64_t>(colL) * ds.cCol;
 
+        // acc is the running fp32 sum; with kCompensated, comp is Kahan's running
+        // compensation and also absorbs the rounding error of every product, so
+        // that acc - comp carries the row sum to roughly twice fp32 precision.
         float acc[VW];
+        float comp[VW];
 #pragma unroll
         for (int v = 0; v < VW; ++v) {
             acc[v] = 0.0f;
+            comp[v] = 0.0f;
         }
         auto issue = [&](int q) {
             const int c = sCol[q];
@@ -281,50 +286,59 @@ SpmmTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ val
             }
             CpAsyncCommit();
         };
-        auto storeRow = [&](int localRow) {
+        auto value = [&](int v) -> double {
+            return kCompensated ? static_cast<double>(acc[v]) - static_cast<double>(comp[v])
+                                : static_cast<double>(acc[v]);
+        };
+        // C[row] = alpha * sum + beta * C[row]; beta == 0 never reads C.
+        auto storeRow = [&](int localRow, const double (&sum)[VW]) {
             if (!colOk) {
                 return;
             }
             float* dst = cLane + static_cast<int64_t>(i0 + localRow) * ds.cRow;
-            if (VW == 1) {
-                dst[0] = sc.betaZero ? sc.alpha * acc[0] : sc.alpha * acc[0] + sc.beta * dst[0];
-            } else {
-                V out;
-                float* o = reinterpret_cast<float*>(&out);
-                if (sc.betaZero) {
-#pragma unroll
-                    for (int v = 0; v < VW; ++v) {
-                        o[v] = sc.alpha * acc[v];
-                    }
-                } else {
-                    const V old = *reinterpret_cast<const V*>(dst);
-                    const float* od = reinterpret_cast<const float*>(&old);
-#pragma unroll
-                    for (int v = 0; v < VW; ++v) {
-                        o[v] = sc.alpha * acc[v] + sc.beta * od[v];
-                    }
-                }
-                *reinterpret_cast<V*>(dst) = out;
+            V old;
+            float* od = reinterpret_cast<float*>(&old);
+            if (!sc.betaZero) {
+                old = *reinterpret_cast<const V*>(dst);
             }
+            V out;
+            float* o = reinterpret_cast<float*>(&out);
+#pragma unroll
+            for (int v = 0; v < VW; ++v) {
+                if (kCompensated) {
+                    const double r = static_cast<double>(sc.alpha) * sum[v];
+                    o[v] = static_cast<float>(sc.betaZero ? r : r + static_cast<double>(sc.beta) * od[v]);
+                } else {
+                    const float f = static_cast<float>(sum[v]);
+                    o[v] = sc.betaZero ? sc.alpha * f : sc.alpha * f + sc.beta * od[v];
+                }
+            }
+            *reinterpret_cast<V*>(dst) = out;
         };
         // A finished row goes to C, unless it is the warp's first row and its
         // beginning lies elsewhere: then it waits in shared memory.
         bool first = true;
         auto flush = [&](int localRow) {
+            double sum[VW];
+#pragma unroll
+            for (int v = 0; v < VW; ++v) {
+                sum[v] = value(v);
+            }
             if (first && headOpen) {
                 if (colOk) {
 #pragma unroll
                     for (int v = 0; v < VW; ++v) {
-                        sHead[warp * kPanel + lane * VW + v] = acc[v];
+                        sHead[warp * kPanel + lane * VW + v] = sum[v];
                     }
                 }
             } else {
-                storeRow(localRow);
+                storeRow(localRow, sum);
             }
             first = false;
 #pragma unroll
             for (int v = 0; v < VW; ++v) {
                 acc[v] = 0.0f;
+                comp[v] = 0.0f;
             }
         };
 
@@ -352,7 +366,16 @@ SpmmTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ val
                 const float* bv = reinterpret_cast<const float*>(&b);
 #pragma unroll
                 for (int v = 0; v < VW; ++v) {
-                    acc[v] = fmaf(a, bv[v], acc[v]);
+                    if (kCompensated) {
+                        const float prod = __fmul_rn(a, bv[v]);
+                        const float err = fmaf(a, bv[v], -prod);  // exact: a*b == prod + err
+                        const float y = __fsub_rn(prod, comp[v]);
+                        const float tsum = __fadd_rn(acc[v], y);
+                        comp[v] = __fsub_rn(__fsub_rn(__fsub_rn(tsum, acc[v]), y), err);
+                        acc[v] = tsum;
+                    } else {
+                        acc[v] = fmaf(a, bv[v], acc[v]);
+                    }
                 }
             }
             if (q + kStages < q1) {
@@ -368,7 +391,7 @@ SpmmTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ val
         if (colOk) {  // what is left belongs to the row that continues past this warp
 #pragma unroll
             for (int v = 0; v < VW; ++v) {
-                sTail[warp * kPanel + lane * VW + v] = acc[v];
+                sTail[warp * kPanel + lane * VW + v] = value(v);
             }
         }
         CpAsyncWait<0>();
@@ -381,23 +404,24 @@ SpmmTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ val
             while (firstWarp > 0 && sWarpRow[firstWarp] == r0) {
                 --firstWarp;
             }
+            double total[VW];
 #pragma unroll
             for (int v = 0; v < VW; ++v) {
-                float sum = 0.0f;
+                double sum = 0.0;
                 for (int u = firstWarp; u < warp; ++u) {
                     sum += sTail[u * kPanel + lane * VW + v];
                 }
-                acc[v] = sum + sHead[warp * kPanel + lane * VW + v];
+                total[v] = sum + sHead[warp * kPanel + lane * VW + v];
             }
             // The chain reaches back to the tile's first item exactly when the
             // row is the tile's first row; then an earlier tile holds more of it.
             if (r0 == 0 && tileHeadOpen) {
 #pragma unroll
                 for (int v = 0; v < VW; ++v) {
-                    tileHead[colL + v] = acc[v];
+                    tileHead[colL + v] = total[v];
                 }
             } else {
-                storeRow(r0);
+                storeRow(r0, total);
             }
         }
         if (warp == kWarps - 1 && colOk) {
@@ -407,7 +431,7 @@ SpmmTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ val
             }
 #pragma unroll
             for (int v = 0; v < VW; ++v) {
-                float sum = 0.0f;
+                double sum = 0.0;
                 for (int u = firstWarp; u < kWarps; ++u) {
                     sum += sTail[u * kPanel + lane * VW + v];
                 }
@@ -447,27 +471,39 @@ __global__ void SpmmCarryFixupKernel(float* __restrict__ C, SpmmPlanView plan, A
         for (int c = lane; c < n; c += 32) {
             double sum = 0.0;
             for (uint32_t u = first; u < t; ++u) {
-                sum += static_cast<double>(plan.carry[static_cast<size_t>(2 * u) * n + c]);
+                sum += plan.carry[static_cast<size_t>(2 * u) * n + c];
             }
-            sum += static_cast<double>(plan.carry[static_cast<size_t>(2 * t + 1) * n + c]);
+            sum += plan.carry[static_cast<size_t>(2 * t + 1) * n + c];
             float* dst = C + static_cast<int64_t>(i0) * ds.cRow + static_cast<int64_t>(c) * ds.cCol;
-            const float s = static_cast<float>(sum);
-            *dst = sc.betaZero ? sc.alpha * s : sc.alpha * s + sc.beta * *dst;
+            const double r = static_cast<double>(sc.alpha) * sum;
+            *dst = static_cast<float>(sc.betaZero ? r : r + static_cast<double>(sc.beta) * *dst);
         }
     }
 }
 
-template <int VW>
+template <int VW, bool kCompensated>
 void Launch(const void* colInd, const void* values, const void* b, void* c, const SpmmPlanView& plan,
             const AclspSpmmParams& p, const DenseStrides& ds, cudaStream_t s)
 {
     constexpr size_t smem = SmemBytes(VW);
     // More than 48 KiB of dynamic shared memory has to be requested per kernel
     // and per device; the attribute is cheap to set, so it is set every time.
-    cudaFuncSetAttribute(SpmmTileKernel<VW>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    SpmmTileKernel<VW><<<plan.numTiles, kThreads, smem, s>>>(
+    cudaFuncSetAttribute(SpmmTileKernel<VW, kCompensated>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         static_cast<int>(smem));
+    SpmmTileKernel<VW, kCompensated><<<plan.numTiles, kThreads, smem, s>>>(
         static_cast<const int32_t*>(colInd), static_cast<const float*>(values), static_cast<const float*>(b),
         static_cast<float*>(c), plan, p, ds);
+}
+
+template <int VW>
+void LaunchByPrecision(const void* colInd, const void* values, const void* b, void* c, const SpmmPlanView& plan,
+                       const AclspSpmmParams& p, const DenseStrides& ds, cudaStream_t s)
+{
+    if (p.highPrecision != 0) {
+        Launch<VW, true>(colInd, values, b, c, plan, p, ds, s);
+    } else {
+        Launch<VW, false>(colInd, values, b, c, plan, p, ds, s);
+    }
 }
 
 }  // namespace
@@ -498,11 +534,11 @@ extern "C" void spmm_b200_kernel_do(const void* colInd, const void* values, cons
         vw = 2;
     }
     if (vw == 4) {
-        Launch<4>(colInd, values, b, c, plan, p, ds, s);
+        LaunchByPrecision<4>(colInd, values, b, c, plan, p, ds, s);
     } else if (vw == 2) {
-        Launch<2>(colInd, values, b, c, plan, p, ds, s);
+        LaunchByPrecision<2>(colInd, values, b, c, plan, p, ds, s);
     } else {
-        Launch<1>(colInd, values, b, c, plan, p, ds, s);
+        LaunchByPrecision<1>(colInd, values, b, c, plan, p, ds, s);
     }
     uint32_t blocks = (plan.numTiles + 7u) / 8u;
     blocks = blocks > 148u * 8u ? 148u * 8u : blocks;

@@ -259,7 +259,12 @@ SpmvTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ val
             const int e = segEnd(k);
             if (e - b >= kLongSegment) {
                 if (lane == 0) {
-                    sLong[atomicAdd(&sNumLong, 1)] = k;
+                    // A valid CSR has at most kMaxLong such pieces per tile; row
+                    // offsets that overlap could claim more, those are dropped.
+                    const int slot = atomicAdd(&sNumLong, 1);
+                    if (slot < kMaxLong) {
+                        sLong[slot] = k;
+                    }
                 }
                 active = false;
             } else {
@@ -279,7 +284,7 @@ SpmvTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ val
     __syncthreads();
 
     // Long pieces: the whole CTA adds one piece, warps combined in warp order.
-    const int numLong = sNumLong;
+    const int numLong = sNumLong < kMaxLong ? sNumLong : kMaxLong;
     for (int q = 0; q < numLong; ++q) {
         const int k = sLong[q];
         const int b = segBegin(k);

@@ -192,7 +192,7 @@ def spmv_plan_layout(rows: int, nnz: int) -> dict:
 
 
 def spmm_plan_layout(rows: int, nnz: int, dense_cols: int) -> dict:
-    return plan_layout(rows, nnz, SPMM_TILE_ITEMS, 8 * dense_cols)
+    return plan_layout(rows, nnz, SPMM_TILE_ITEMS, 16 * dense_cols)
 
 
 def plan_tiles(row_ptr_n, nnz: int, tile_items: int, class_div: int):

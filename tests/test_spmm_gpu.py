@@ -17,9 +17,25 @@ from tests.gpu_util import SpmmCase, dev, random_csr  # noqa: E402
 RTOL, ATOL = 1e-5, 1e-6
 
 
+HP = L.SPMM_CSR_FP32_HIGH_PRECISION_ALG
+
+
 def assert_close(got, truth, what=""):
     bad, max_abs, max_rel = O.check_tolerance(got, truth, RTOL, ATOL)
     assert bad == 0, f"{what}: {bad} of {got.size} outside tolerance (max abs {max_abs:.3e}, max rel {max_rel:.3e})"
+
+
+def assert_fp32_forward_bound(got, truth, rp, ci, va, b, alpha, beta, c0, what=""):
+    """Plain fp32 accumulation, in any order, obeys the classical forward bound of a dot product:
+    |got - truth| <= (len + 4) * 2^-24 * (|alpha| * |A||B| + |beta| * |C|), element by element.  The
+    default algorithm (and the reference's own fp32 golden) is held to this; the reference's relative
+    bar (test/spmm/arch35/spmm_test.cpp:330-378) cannot be used on cancelling rows."""
+    n = b.shape[1]
+    mag = O.spmm_f64(rp, ci, np.abs(va), np.abs(b), n, np.abs(c0), n, n, b.shape[0], abs(alpha), abs(beta))
+    lens = np.diff(rp)[:, None]
+    bound = (lens + 4) * 2.0 ** -24 * mag + 1e-30
+    err = np.abs(got.astype(np.float64) - truth)
+    assert (err <= bound).all(), f"{what}: worst err/bound {np.max(err / bound):.3f}"
 
 
 def test_reference_known_answers(kats):
@@ -34,9 +50,16 @@ def test_reference_known_answers(kats):
 def test_reference_goldens(goldens):
     for name, g in goldens.items():
         n = g["n"]
-        case = SpmmCase(g["row_ptr"], g["col_ind"], g["values"], g["cols"], n, g["b"], n, g["c0"], n, base=g["base"])
+        # the compensated algorithm meets the strict tolerance on any data, cancelling rows included
+        case = SpmmCase(g["row_ptr"], g["col_ind"], g["values"], g["cols"], n, g["b"], n, g["c0"], n, base=g["base"],
+                        alg=HP)
         got = case.run(g["alpha"], g["beta"]).reshape(g["rows"], n)
         assert_close(got, g["truth"], name)
+        # the default algorithm accumulates in plain fp32, like the reference's default and its fp32 golden
+        case = SpmmCase(g["row_ptr"], g["col_ind"], g["values"], g["cols"], n, g["b"], n, g["c0"], n, base=g["base"])
+        got = case.run(g["alpha"], g["beta"]).reshape(g["rows"], n)
+        assert_fp32_forward_bound(got, g["truth"], g["row_ptr"] - g["base"], g["col_ind"] - g["base"], g["values"],
+                                  g["b"], g["alpha"], g["beta"], g["c0"], name)
 
 
 def layout(a, row_major, pad):
@@ -91,7 +114,7 @@ def test_layout_and_scalar_matrix(case):
     c_store, ldc = layout(c0, c_row, pad_c)
     sc = SpmmCase(rp + base, ci + base, va, k, n, b_store, ldb, c_store, ldc, base=base,
                   order_b=L.ORDER_ROW if b_row else L.ORDER_COL, order_c=L.ORDER_ROW if c_row else L.ORDER_COL,
-                  op_b=L.OP_T if op_t else L.OP_N)
+                  op_b=L.OP_T if op_t else L.OP_N, alg=HP)
     got_store = sc.run(alpha, beta, preprocess=pre)
     truth = O.spmm_f64(rp, ci, va, b, n, c0, n, n, k, alpha, beta)
     assert_close(unlayout(got_store, m, n, ldc, c_row), truth, name)
@@ -103,7 +126,14 @@ def test_layout_and_scalar_matrix(case):
     # the oracle's fp32 golden of the same stored layout agrees too
     gold = O.spmm_f32(rp, ci, va, b_store, ldb, c_store, ldc, n, alpha, beta, b_row_major=b_row,
                       op_b_transpose=op_t, c_row_major=c_row)
-    assert_close(unlayout(gold, m, n, ldc, c_row), truth, name + " (fp32 golden)")
+    assert_fp32_forward_bound(unlayout(gold, m, n, ldc, c_row), truth, rp, ci, va, b, alpha, beta, c0,
+                              name + " (fp32 golden)")
+    # and so does the default (plain fp32) algorithm on the same storage
+    sd = SpmmCase(rp + base, ci + base, va, k, n, b_store, ldb, c_store, ldc, base=base,
+                  order_b=L.ORDER_ROW if b_row else L.ORDER_COL, order_c=L.ORDER_ROW if c_row else L.ORDER_COL,
+                  op_b=L.OP_T if op_t else L.OP_N)
+    assert_fp32_forward_bound(unlayout(sd.run(alpha, beta, preprocess=pre), m, n, ldc, c_row), truth, rp, ci, va, b,
+                              alpha, beta, c0, name)
 
 
 def test_device_scalars_and_plan_reuse():
@@ -113,7 +143,7 @@ def test_device_scalars_and_plan_reuse():
     va = rng.uniform(-1, 1, ci.size).astype(np.float32)
     b = rng.uniform(-1, 1, (k, n)).astype(np.float32)
     c0 = rng.uniform(-1, 1, (m, n)).astype(np.float32)
-    sc = SpmmCase(rp, ci, va, k, n, b, n, c0, n)
+    sc = SpmmCase(rp, ci, va, k, n, b, n, c0, n, alg=HP)
     sc.handle.set_pointer_mode(L.POINTER_MODE_DEVICE)
     alpha, beta = dev(np.array([0.75], np.float32)), dev(np.array([-0.25], np.float32))
     got = sc.run(alpha, beta, preprocess=False).reshape(m, n)
@@ -179,8 +209,11 @@ def test_long_and_empty_rows_all_widths(n):
     va = rng.uniform(-1, 1, ci.size).astype(np.float32)
     b = rng.uniform(-1, 1, (k, n)).astype(np.float32)
     c0 = rng.uniform(-1, 1, (m, n)).astype(np.float32)
+    truth = O.spmm_f64(rp, ci, va, b, n, c0, n, n, k, 1.5, -0.5)
+    got = SpmmCase(rp, ci, va, k, n, b, n, c0, n, alg=HP).run(1.5, -0.5).reshape(m, n)
+    assert_close(got, truth, f"n={n} compensated")
     got = SpmmCase(rp, ci, va, k, n, b, n, c0, n).run(1.5, -0.5).reshape(m, n)
-    assert_close(got, O.spmm_f64(rp, ci, va, b, n, c0, n, n, k, 1.5, -0.5), f"n={n}")
+    assert_fp32_forward_bound(got, truth, rp, ci, va, b, 1.5, -0.5, c0, f"n={n} default")
 
 
 def test_shared_workspace_between_spmv_and_spmm(kats):
