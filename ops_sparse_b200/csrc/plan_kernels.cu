@@ -134,7 +134,7 @@ void AclspLaunchPlanBuild(const void* rowPtr, void* workspace, uint32_t rows, ui
 {
     AclspPlanLayout layout;
     uint32_t tileItems = ACLSP_SPMV_TILE_ITEMS;
-    uint32_t classDiv = 4u;
+    uint32_t classDiv = ACLSP_SPMV_CLASS_DIV;
     if (kind == ACLSP_KIND_SPMM) {
         aclspSpmmLayout(rows, nnz, denseCols, &layout);
         tileItems = ACLSP_SPMM_TILE_ITEMS;

@@ -42,6 +42,11 @@
 #define ACLSP_SPMV_TILE_ITEMS 2048u
 #define ACLSP_SPMM_TILE_ITEMS 1024u
 
+/* SpMV row bins: a lane adds about this many products of an average row.
+ * Products are summed out of shared memory, where a long serial run per lane
+ * costs the fewest instructions; short rows therefore get one lane each. */
+#define ACLSP_SPMV_CLASS_DIV 16u
+
 /* Highest row-bin code: 2^5 = 32 lanes (one warp) per row. */
 #define ACLSP_MAX_CLASS 5u
 
@@ -109,7 +114,7 @@ static inline ACLSP_HD void aclspSpmmLayout(uint64_t rows, uint64_t nnz, uint64_
 
 /* Row bin of a tile with `nr` completed rows and `nt` non-zeros: the number
  * of lanes that cooperate on one row is 2^class, chosen so that a lane adds
- * about four products of an average row.  `div` is 4 for SpMV. */
+ * about `div` products of an average row. */
 static inline ACLSP_HD uint32_t aclspTileClass(uint32_t nr, uint32_t nt, uint32_t div)
 {
     const uint32_t avg = nt / (nr + 1u);

@@ -8,7 +8,9 @@
  * tile:
  *   1. the tile's slice of colInd / values is streamed with 128-bit loads
  *      (evict-first: it is read exactly once), x[col] is gathered through the
- *      read-only path, and the exact fp64 products are staged in shared memory;
+ *      read-only path, and every product is staged in shared memory as an
+ *      exact pair of floats (rounded product, rounding error) with 128-bit,
+ *      conflict-free stores;
  *   2. rows that end inside the tile are reduced by groups of 2^class lanes
  *      ("vector per row", class picked per tile by the preprocessing pass from
  *      the tile's mean row length; class 5 is warp per row) with a shuffle
@@ -20,7 +22,8 @@
  *      in tile order and writes that row.
  * Every sum is taken in a fixed order, so results are bit-reproducible.
  *
- * Accuracy.  fp32 x fp32 products are exact in fp64 and all sums are fp64, so
+ * Accuracy.  Every product is kept exactly (hi + lo) and the hi parts are summed
+ * in fp64 (the lo parts, 2^-24 of the products, in fp32), so
  * a row is as accurate as the reference's host golden (SpmvCpu with a double
  * accumulator, test/spmv/arch22/spmv_test.cpp:258-279,309-348) up to the order
  * of the additions; the reference's device kernels reach for compensated
@@ -43,7 +46,7 @@ namespace {
 constexpr int kThreads = 256;
 constexpr int kWarps = kThreads / 32;
 constexpr int kTile = ACLSP_SPMV_TILE_ITEMS;
-constexpr int kLongSegment = 512;
+constexpr int kLongSegment = 256;
 constexpr int kMaxLong = kTile / kLongSegment;
 
 struct SpmvPlanView {
@@ -99,14 +102,21 @@ __device__ __forceinline__ void StoreRow(float* __restrict__ y, int64_t index, d
     y[index] = static_cast<float>(r);
 }
 
-__device__ __forceinline__ double Product(float a, int32_t rawCol, const float* __restrict__ x, uint32_t base,
-                                          uint32_t cols, int64_t xStride)
+// One product as an unevaluated sum hi + lo of two floats: hi is the rounded
+// fp32 product and lo its exact rounding error, so hi + lo == a * x[col]
+// exactly.  Entries whose column is out of range contribute nothing.
+__device__ __forceinline__ void Product(float a, int32_t rawCol, const float* __restrict__ x, uint32_t base,
+                                        uint32_t cols, int64_t xStride, float& hi, float& lo)
 {
     const uint32_t c = static_cast<uint32_t>(rawCol) - base;
     if (c >= cols) {
-        return 0.0;
+        hi = 0.0f;
+        lo = 0.0f;
+        return;
     }
-    return static_cast<double>(a) * static_cast<double>(__ldg(x + static_cast<int64_t>(c) * xStride));
+    const float xv = __ldg(x + static_cast<int64_t>(c) * xStride);
+    hi = __fmul_rn(a, xv);
+    lo = fmaf(a, xv, -hi);
 }
 
 template <bool kVector>
@@ -114,9 +124,10 @@ __global__ void __launch_bounds__(kThreads)
 SpmvTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ values, const float* __restrict__ x,
                float* __restrict__ y, SpmvPlanView plan, AclspSpmvParams p)
 {
-    // Products first, the tile's row offsets packed against the end: a tile
-    // has nt products and nr + 1 offsets with nt + nr <= kTile.
-    __shared__ double sProd[kTile + 2];
+    // One pool of 32-bit words: the hi parts of the tile's products, their lo
+    // parts, and the tile's row offsets packed against the end.  A tile has nt
+    // products and nr + 1 offsets with nt + nr <= kTile.
+    __shared__ __align__(16) float sPool[2 * kTile + 24];
     __shared__ double sWarp[kWarps];
     __shared__ int sLong[kMaxLong];
     __shared__ int sNumLong;
@@ -144,7 +155,14 @@ SpmvTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ val
         }
         return;
     }
-    int* sOff = reinterpret_cast<int*>(sProd + kTile + 2) - (nr + 2);
+    // Products are stored at their offset from the 4-aligned array index a0,
+    // so that a 128-bit load of the arrays maps onto a 128-bit shared store.
+    const int a0 = kVector ? (j0 & ~3) : j0;
+    const int shift = j0 - a0;
+    const int span = (nt + shift + 3) & ~3;
+    float* sHi = sPool;
+    float* sLo = sPool + span;
+    int* sOff = reinterpret_cast<int*>(sPool + 2 * kTile + 24) - (nr + 2);
     if (tid == 0) {
         sNumLong = 0;
     }
@@ -153,43 +171,39 @@ SpmvTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ val
     }
 
     if (kVector) {
-        // Vectors are aligned to 4 elements of the arrays, not of the tile.
-        const int a0 = j0 & ~3;
-        const int nvec = (j1 - a0 + 3) >> 2;
+        const int nvec = span >> 2;
         struct Vec4 {
-            int32_t c[4];
-            float w[4];
+            int4 c;
+            float4 w;
         };
         auto loadVec = [&](int v, Vec4& o) {
             const int e = a0 + 4 * v;
             if (e + 4 <= nnz) {
-                const int4 cv = __ldcs(reinterpret_cast<const int4*>(colInd + e));
-                const float4 wv = __ldcs(reinterpret_cast<const float4*>(values + e));
-                o.c[0] = cv.x; o.c[1] = cv.y; o.c[2] = cv.z; o.c[3] = cv.w;
-                o.w[0] = wv.x; o.w[1] = wv.y; o.w[2] = wv.z; o.w[3] = wv.w;
+                o.c = __ldcs(reinterpret_cast<const int4*>(colInd + e));
+                o.w = __ldcs(reinterpret_cast<const float4*>(values + e));
             } else {  // the last vector of the arrays may be partial
+                int32_t c[4];
+                float w[4];
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
                     const bool in = e + q < nnz;
-                    o.c[q] = in ? __ldcs(colInd + e + q) : -1;
-                    o.w[q] = in ? __ldcs(values + e + q) : 0.0f;
+                    c[q] = in ? __ldcs(colInd + e + q) : -1;
+                    w[q] = in ? __ldcs(values + e + q) : 0.0f;
                 }
+                o.c = make_int4(c[0], c[1], c[2], c[3]);
+                o.w = make_float4(w[0], w[1], w[2], w[3]);
             }
         };
+        // Elements of the first and last vector that belong to a neighbouring
+        // tile are multiplied too; nothing reads their slots.
         auto useVec = [&](int v, const Vec4& o) {
-            const int k0 = a0 + 4 * v - j0;
-            double pr[4];
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                pr[q] = Product(o.w[q], o.c[q], x, p.indexBase, p.cols, 1);
-            }
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                const int k = k0 + q;
-                if (k >= 0 && k < nt) {
-                    sProd[k] = pr[q];
-                }
-            }
+            float4 hi, lo;
+            Product(o.w.x, o.c.x, x, p.indexBase, p.cols, 1, hi.x, lo.x);
+            Product(o.w.y, o.c.y, x, p.indexBase, p.cols, 1, hi.y, lo.y);
+            Product(o.w.z, o.c.z, x, p.indexBase, p.cols, 1, hi.z, lo.z);
+            Product(o.w.w, o.c.w, x, p.indexBase, p.cols, 1, hi.w, lo.w);
+            *reinterpret_cast<float4*>(sHi + 4 * v) = hi;
+            *reinterpret_cast<float4*>(sLo + 4 * v) = lo;
         };
         // A tile spans at most kTile / 4 + 1 vectors: two per thread, both
         // loads in flight before either is used, plus a one-vector remainder.
@@ -216,8 +230,8 @@ SpmvTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ val
     } else {
         for (int k = tid; k < nt; k += kThreads) {
             const int64_t e = static_cast<int64_t>(j0) + k;
-            sProd[k] = Product(values[e * p.valuesStride], colInd[e * p.colIndStride], x, p.indexBase, p.cols,
-                               p.xStride);
+            Product(values[e * p.valuesStride], colInd[e * p.colIndStride], x, p.indexBase, p.cols, p.xStride,
+                    sHi[k], sLo[k]);
         }
     }
     __syncthreads();
@@ -225,6 +239,8 @@ SpmvTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ val
     const Scalars sc = LoadScalars(p);
     const bool headOpen = sOff[0] < 0;  // row i0 began in an earlier tile
     const int nseg = nr + 1;            // rows ending here, then the open tail
+    const float* hiT = sHi + shift;     // product k of the tile
+    const float* loT = sLo + shift;
 
     auto segBegin = [&](int k) { const int b = sOff[k]; return b < 0 ? 0 : (b > nt ? nt : b); };
     auto segEnd = [&](int k) {
@@ -243,13 +259,25 @@ SpmvTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ val
             StoreRow(y, static_cast<int64_t>(i0 + k) * p.yStride, sum, sc);
         }
     };
+    // Sum of products [b, e) taken by this thread with the given stride: the hi
+    // parts in fp64, the (tiny) lo parts in fp32, joined at the end.
+    auto strided = [&](int b, int e, int first, int stride) {
+        double hi = 0.0;
+        float lo = 0.0f;
+        for (int q = b + first; q < e; q += stride) {
+            hi += static_cast<double>(hiT[q]);
+            lo += loT[q];
+        }
+        return hi + static_cast<double>(lo);
+    };
 
     // Vector per row: 2^cls lanes share a row piece.
     const int cls = plan.tileClass[t] & 7;
-    const int lanes = 1 << (cls > 5 ? 5 : cls);
+    const int shiftLanes = cls > 5 ? 5 : cls;
+    const int lanes = 1 << shiftLanes;
     const int lane = tid & (lanes - 1);
-    const int group = tid >> (cls > 5 ? 5 : cls);
-    const int ngroups = kThreads / lanes;
+    const int group = tid >> shiftLanes;
+    const int ngroups = kThreads >> shiftLanes;
     for (int k0 = 0; k0 < nseg; k0 += ngroups) {
         const int k = k0 + group;
         bool active = k < nseg;
@@ -268,9 +296,7 @@ SpmvTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ val
                 }
                 active = false;
             } else {
-                for (int q = b + lane; q < e; q += lanes) {
-                    sum += sProd[q];
-                }
+                sum = strided(b, e, lane, lanes);
             }
         }
         __syncwarp();
@@ -287,12 +313,7 @@ SpmvTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ val
     const int numLong = sNumLong < kMaxLong ? sNumLong : kMaxLong;
     for (int q = 0; q < numLong; ++q) {
         const int k = sLong[q];
-        const int b = segBegin(k);
-        const int e = segEnd(k);
-        double sum = 0.0;
-        for (int i = b + tid; i < e; i += kThreads) {
-            sum += sProd[i];
-        }
+        double sum = strided(segBegin(k), segEnd(k), tid, kThreads);
         for (int o = 16; o > 0; o >>= 1) {
             sum += __shfl_xor_sync(0xffffffffu, sum, o);
         }

@@ -167,6 +167,7 @@ def greedy_row_bin_pack(row_nnz, bins: int):
 
 SPMV_TILE_ITEMS = 2048
 SPMM_TILE_ITEMS = 1024
+SPMV_CLASS_DIV = 16
 HEADER_BYTES = 192
 PLAN_MAGIC = 0x30303242
 

@@ -132,7 +132,7 @@ def test_plan_twin_invariants():
                  np.array([30000]), np.array([0, 0, 5000, 0])):
         rp = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
         nnz, rows = int(rp[-1]), lens.size
-        for tile, div in ((2048, 4), (1024, 1)):
+        for tile, div in ((2048, 16), (1024, 1)):
             tile_row, tile_class = O.plan_tiles(rp, nnz, tile, div)
             nt = tile_row.size - 1
             assert nt == (rows + nnz + tile - 1) // tile

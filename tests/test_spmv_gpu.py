@@ -115,7 +115,7 @@ def test_plan_metadata_bit_exact():
             rows = len(lengths)
             got_rp = ws[lay["row_ptr_off"]:lay["row_ptr_off"] + 4 * (rows + 1)].view(np.int32)
             assert np.array_equal(got_rp, O.normalize_row_offsets(rp + base, rows, base))
-            tile_row, tile_class = O.plan_tiles(rp, nnz, O.SPMV_TILE_ITEMS, 4)
+            tile_row, tile_class = O.plan_tiles(rp, nnz, O.SPMV_TILE_ITEMS, O.SPMV_CLASS_DIV)
             nt = lay["num_tiles"]
             assert np.array_equal(ws[lay["tile_row_off"]:lay["tile_row_off"] + 4 * (nt + 1)].view(np.int32), tile_row)
             assert np.array_equal(ws[lay["tile_class_off"]:lay["tile_class_off"] + 4 * nt].view(np.int32), tile_class)
