@@ -35,6 +35,7 @@
  * sparse/spmm/arch35/kernel/spmm_kernel_simt.cpp:406-434 clamps alike).
  */
 #include <cstdint>
+#include <cstdlib>
 
 #include <cuda_runtime.h>
 
@@ -157,7 +158,7 @@ constexpr size_t SmemBytes(int vw)
            + sizeof(int) * (2 * kWarps + 2);            // warp row split, head flags
 }
 
-template <int VW, bool kCompensated>
+template <int VW, bool kCompensated, bool kStageB>
 __global__ void __launch_bounds__(kThreads)
 SpmmTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ values, const float* __restrict__ B,
                float* __restrict__ C, SpmmPlanView plan, AclspSpmmParams p, DenseStrides ds)
@@ -344,44 +345,82 @@ SpmmTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ val
 
         int row = r0;
         int rowEnd = row < nr ? sOff[row + 1] : nt + 1;  // the open tail row never ends here
+        auto accumulate = [&](float a, const V& b) {
+            const float* bv = reinterpret_cast<const float*>(&b);
 #pragma unroll
-        for (int s = 0; s < kStages; ++s) {
-            if (q0 + s < q1) {
-                issue(q0 + s);
-            } else {
-                CpAsyncCommit();
-            }
-        }
-        for (int q = q0; q < q1; ++q) {
-            while (rowEnd <= q && row < r1) {
-                flush(row);
-                ++row;
-                rowEnd = row < nr ? sOff[row + 1] : nt + 1;
-            }
-            CpAsyncWait<kStages - 1>();
-            const int c = sCol[q];
-            if (c >= 0 && colOk) {
-                const V b = *reinterpret_cast<const V*>(ring + (q % kStages) * kPanel);
-                const float a = sVal[q];
-                const float* bv = reinterpret_cast<const float*>(&b);
-#pragma unroll
-                for (int v = 0; v < VW; ++v) {
-                    if (kCompensated) {
-                        const float prod = __fmul_rn(a, bv[v]);
-                        const float err = fmaf(a, bv[v], -prod);  // exact: a*b == prod + err
-                        const float y = __fsub_rn(prod, comp[v]);
-                        const float tsum = __fadd_rn(acc[v], y);
-                        comp[v] = __fsub_rn(__fsub_rn(__fsub_rn(tsum, acc[v]), y), err);
-                        acc[v] = tsum;
-                    } else {
-                        acc[v] = fmaf(a, bv[v], acc[v]);
-                    }
+            for (int v = 0; v < VW; ++v) {
+                if (kCompensated) {
+                    const float prod = __fmul_rn(a, bv[v]);
+                    const float err = fmaf(a, bv[v], -prod);  // exact: a*b == prod + err
+                    const float y = __fsub_rn(prod, comp[v]);
+                    const float tsum = __fadd_rn(acc[v], y);
+                    comp[v] = __fsub_rn(__fsub_rn(__fsub_rn(tsum, acc[v]), y), err);
+                    acc[v] = tsum;
+                } else {
+                    acc[v] = fmaf(a, bv[v], acc[v]);
                 }
             }
-            if (q + kStages < q1) {
-                issue(q + kStages);
-            } else {
-                CpAsyncCommit();
+        };
+        if (kStageB) {
+#pragma unroll
+            for (int s = 0; s < kStages; ++s) {
+                if (q0 + s < q1) {
+                    issue(q0 + s);
+                } else {
+                    CpAsyncCommit();
+                }
+            }
+            for (int q = q0; q < q1; ++q) {
+                while (rowEnd <= q && row < r1) {
+                    flush(row);
+                    ++row;
+                    rowEnd = row < nr ? sOff[row + 1] : nt + 1;
+                }
+                CpAsyncWait<kStages - 1>();
+                const int c = sCol[q];
+                if (c >= 0 && colOk) {
+                    accumulate(sVal[q], *reinterpret_cast<const V*>(ring + (q % kStages) * kPanel));
+                }
+                if (q + kStages < q1) {
+                    issue(q + kStages);
+                } else {
+                    CpAsyncCommit();
+                }
+            }
+        } else {
+            // Rows of B straight into registers, kUnroll gathers in flight per lane.
+            constexpr int kUnroll = 4;
+            for (int q = q0; q < q1; q += kUnroll) {
+                V b[kUnroll];
+                float a[kUnroll];
+#pragma unroll
+                for (int u = 0; u < kUnroll; ++u) {
+                    const int qq = q + u;
+                    const int c = qq < q1 ? sCol[qq] : -1;
+                    const bool ok = c >= 0 && colOk;
+                    a[u] = ok ? sVal[qq] : 0.0f;
+                    if (ok) {
+                        b[u] = __ldg(reinterpret_cast<const V*>(bLane + static_cast<int64_t>(c) * ds.bRow));
+                    } else {
+                        float* z = reinterpret_cast<float*>(&b[u]);
+#pragma unroll
+                        for (int v = 0; v < VW; ++v) {
+                            z[v] = 0.0f;
+                        }
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < kUnroll; ++u) {
+                    const int qq = q + u;
+                    if (qq < q1) {
+                        while (rowEnd <= qq && row < r1) {
+                            flush(row);
+                            ++row;
+                            rowEnd = row < nr ? sOff[row + 1] : nt + 1;
+                        }
+                        accumulate(a[u], b[u]);
+                    }
+                }
             }
         }
         while (row < r1) {
@@ -481,16 +520,16 @@ __global__ void SpmmCarryFixupKernel(float* __restrict__ C, SpmmPlanView plan, A
     }
 }
 
-template <int VW, bool kCompensated>
+template <int VW, bool kCompensated, bool kStageB>
 void Launch(const void* colInd, const void* values, const void* b, void* c, const SpmmPlanView& plan,
             const AclspSpmmParams& p, const DenseStrides& ds, cudaStream_t s)
 {
     constexpr size_t smem = SmemBytes(VW);
     // More than 48 KiB of dynamic shared memory has to be requested per kernel
     // and per device; the attribute is cheap to set, so it is set every time.
-    cudaFuncSetAttribute(SpmmTileKernel<VW, kCompensated>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaFuncSetAttribute(SpmmTileKernel<VW, kCompensated, kStageB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                          static_cast<int>(smem));
-    SpmmTileKernel<VW, kCompensated><<<plan.numTiles, kThreads, smem, s>>>(
+    SpmmTileKernel<VW, kCompensated, kStageB><<<plan.numTiles, kThreads, smem, s>>>(
         static_cast<const int32_t*>(colInd), static_cast<const float*>(values), static_cast<const float*>(b),
         static_cast<float*>(c), plan, p, ds);
 }
@@ -499,10 +538,23 @@ template <int VW>
 void LaunchByPrecision(const void* colInd, const void* values, const void* b, void* c, const SpmmPlanView& plan,
                        const AclspSpmmParams& p, const DenseStrides& ds, cudaStream_t s)
 {
+    // Rows of B are staged in shared memory with cp.async by default;
+    // ACLSPARSE_SPMM_STAGE_B=0 selects the variant that reads them straight into
+    // registers (both run at the same speed on the gather-bound configurations).
+    static const bool stage = [] {
+        const char* e = std::getenv("ACLSPARSE_SPMM_STAGE_B");
+        return e == nullptr || e[0] != '0';
+    }();
     if (p.highPrecision != 0) {
-        Launch<VW, true>(colInd, values, b, c, plan, p, ds, s);
+        if (stage) {
+            Launch<VW, true, true>(colInd, values, b, c, plan, p, ds, s);
+        } else {
+            Launch<VW, true, false>(colInd, values, b, c, plan, p, ds, s);
+        }
+    } else if (stage) {
+        Launch<VW, false, true>(colInd, values, b, c, plan, p, ds, s);
     } else {
-        Launch<VW, false>(colInd, values, b, c, plan, p, ds, s);
+        Launch<VW, false, false>(colInd, values, b, c, plan, p, ds, s);
     }
 }
 
