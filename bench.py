@@ -302,6 +302,8 @@ def run_ours(args, cfg):
                "what": "pinned host x (or B) -> device, aclsparseSpMV/SpMM, y (or C) -> pinned host; A resident"}
 
     clocks = sampler.stop() if rank == 0 else None
+    if world > 1:
+        dist.barrier()  # last collective: every rank reaches it before any rank leaves
     if rank != 0:
         return
     peak, peak_kind = measured_peak()
@@ -340,8 +342,6 @@ def run_ours(args, cfg):
                       "passes, single thread, the reference's host golden restated in oracle/oracle.c",
             "host_cores_available": os.cpu_count()}
     print(json.dumps(line))
-    if world > 1:
-        dist.barrier()
 
 
 def main():
