@@ -15,9 +15,9 @@
  *    alpha or beta reuses it (the reference rebuilds, spmm_host.cpp:63-97,199-215);
  *  - every algorithm value selects the same kernels, which add in a fixed
  *    order (so all of them are deterministic, as the reference's CSR_ALG3 is);
- *    FP32_HIGH_PRECISION additionally compensates the fp32 accumulation, as the
- *    reference's Kahan variant does (spmm_kernel_simt.cpp:424-431), here together
- *    with the rounding error of every product.
+ *    FP32_HIGH_PRECISION additionally compensates the fp32 accumulation (the
+ *    reference's variant is Kahan, spmm_kernel_simt.cpp:424-431; this one is Dot2:
+ *    error-free products and error-free sums, which also holds in cancelling rows).
  */
 #include <cstdint>
 #include <limits>

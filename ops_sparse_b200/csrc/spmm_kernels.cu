@@ -270,9 +270,9 @@ SpmmTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ val
         const float* bLane = B + static_cast<int64_t>(colL) * ds.bCol;
         float* cLane = C + static_cast<int64_t>(colL) * ds.cCol;
 
-        // acc is the running fp32 sum; with kCompensated, comp is Kahan's running
-        // compensation and also absorbs the rounding error of every product, so
-        // that acc - comp carries the row sum to roughly twice fp32 precision.
+        // acc is the running fp32 sum; with kCompensated, comp collects the rounding
+        // errors of every addition and every product, so that acc + comp carries
+        // the row sum to roughly twice fp32 precision.
         float acc[VW];
         float comp[VW];
 #pragma unroll
@@ -288,7 +288,7 @@ SpmmTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ val
             CpAsyncCommit();
         };
         auto value = [&](int v) -> double {
-            return kCompensated ? static_cast<double>(acc[v]) - static_cast<double>(comp[v])
+            return kCompensated ? static_cast<double>(acc[v]) + static_cast<double>(comp[v])
                                 : static_cast<double>(acc[v]);
         };
         // C[row] = alpha * sum + beta * C[row]; beta == 0 never reads C.
@@ -350,11 +350,16 @@ SpmmTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ val
 #pragma unroll
             for (int v = 0; v < VW; ++v) {
                 if (kCompensated) {
+                    // Dot2 (Ogita, Rump, Oishi): error-free product and error-free sum,
+                    // both errors collected in comp; acc + comp is the dot product as if
+                    // accumulated in twice the working precision.  TwoSum, unlike Kahan's
+                    // shortcut, is exact whatever the magnitudes, i.e. also while a row cancels.
                     const float prod = __fmul_rn(a, bv[v]);
-                    const float err = fmaf(a, bv[v], -prod);  // exact: a*b == prod + err
-                    const float y = __fsub_rn(prod, comp[v]);
-                    const float tsum = __fadd_rn(acc[v], y);
-                    comp[v] = __fsub_rn(__fsub_rn(__fsub_rn(tsum, acc[v]), y), err);
+                    const float perr = fmaf(a, bv[v], -prod);  // a*b == prod + perr
+                    const float tsum = __fadd_rn(acc[v], prod);
+                    const float bp = __fsub_rn(tsum, acc[v]);
+                    const float serr = __fadd_rn(__fsub_rn(acc[v], __fsub_rn(tsum, bp)), __fsub_rn(prod, bp));
+                    comp[v] = __fadd_rn(comp[v], __fadd_rn(serr, perr));
                     acc[v] = tsum;
                 } else {
                     acc[v] = fmaf(a, bv[v], acc[v]);
