@@ -23,6 +23,22 @@ extern "C" {
 aclsparseStatus_t aclsparseB200RowBlockBounds(aclsparseHandle_t handle, aclsparseConstSpMatDescr_t matA, int parts,
                                               void* bounds);
 
+/* y = alpha * A * x + beta * y for a CSR matrix (int32 indices, fp32 data, unit strides, host scalars)
+ * WITHOUT an external buffer and without allocating anything: the plan and the per-tile carries that
+ * aclsparseSpMV keeps in the caller's buffer live in an 8 MiB device array built into the library.
+ * For callers that cannot allocate device memory when they need the product - a latency-critical loop
+ * whose memory was fixed at start-up, a host framework whose allocator owns the device, a plug-in that
+ * is only handed its operands.  Asynchronous on `stream`.
+ *   - Matrices whose plan exceeds the built-in scratch (roughly rows * 4 + (rows + nnz) * 0.012 bytes
+ *     > 8 MiB) are refused with ACL_SPARSE_STATUS_INSUFFICIENT_RESOURCES and a message on stderr.
+ *   - The first call on a device looks up the scratch's device address; make it outside stream capture.
+ *   - All calls on a device share the scratch: calls that overlap on the GPU race; keep them in stream order.
+ * This entry point has no counterpart in the reference. */
+aclsparseStatus_t aclsparseB200SpMVNoAlloc(aclrtStream stream, int64_t rows, int64_t cols, int64_t nnz,
+                                           const int32_t* rowOffsets, const int32_t* colInd, const float* values,
+                                           aclsparseIndexBase_t idxBase, const float* x, float* y, float alpha,
+                                           float beta);
+
 #ifdef __cplusplus
 }
 #endif

@@ -127,6 +127,7 @@ SIGNATURES = {
     "aclsparseSpMM": [_P, c_int, c_int, _P, _P, _P, _P, _P, c_int, c_int, _P],
     # include/aclsparse_b200_ext.h
     "aclsparseB200RowBlockBounds": [_P, _P, c_int, _P],
+    "aclsparseB200SpMVNoAlloc": [_P, c_int64, c_int64, c_int64, _P, _P, _P, c_int, _P, _P, c_float, c_float],
     # include/aclsparse_b200_kernels.h
     "spmv_b200_preprocess_kernel_do": [_P, _P, c_uint32, c_uint32, c_uint32, c_int32, c_int64, _P],
     "spmv_b200_kernel_do": [_P, _P, _P, _P, _P, POINTER(SpmvParams), _P],
