@@ -190,7 +190,7 @@ def run_ours(args, cfg):
     if world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torchrun --nproc-per-node N")
     spmv = cfg["kind"] == "spmv"
-    op = (sharded.ShardedSpMV if spmv else sharded.ShardedSpMM)(cfg, rank, world, device)
+    op = (sharded.ShardedSpMV if spmv else sharded.ShardedSpMM)(cfg, rank, world, device, gather=args.gather)
     alpha, beta = cfg["alpha"], cfg["beta"]
     out0 = torch.from_numpy(cfg["y"] if spmv else cfg["c"])
     local0 = out0[op.r0:op.r1].to(device)
@@ -316,12 +316,13 @@ def run_ours(args, cfg):
         "scaling": "strong", "vs_baseline": None, "dtype": "f32 data, f64 accumulate" if spmv else "f32",
         "data": "synthetic",
         "config": {"workload": describe(cfg), "sharding": f"row blocks by nnz over {world} GPU(s), x/B replicated, "
-                   "all-gather of y/C inside the step", "l2": "inputs larger than L2 (matrix streamed from HBM every "
+                   f"reassembly of y/C inside the step ({op.gather_mode if world > 1 else 'none at 1 GPU'})", "l2": "inputs larger than L2 (matrix streamed from HBM every "
                    "step); no flush", "per_step_ms_min_median_max": [float(np.min(per_step)),
                                                                      float(np.median(per_step)),
                                                                      float(np.max(per_step))]},
         "clocks": clocks,
-        "gpu_launches": 2 * args.steps,  # tile kernel + carry fix-up kernel per timed step and rank
+        # tile kernel + carry fix-up kernel (+ the push kernel at N > 1) per timed step and rank
+        "gpu_launches": (3 if world > 1 and op.gather_mode == "push" else 2) * args.steps,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                      "frac": achieved / peak if achieved else None, "traffic": None, "peak_kind": peak_kind,
                      "algorithmic_bytes_per_launch": abytes, "kernel_ms": k_ms,
@@ -355,6 +356,8 @@ def main():
     ap.add_argument("--check-rows", type=int, default=1 << 20, help="rows compared with the oracle before timing")
     ap.add_argument("--cpu-rows", type=int, default=1 << 22, help="row block the CPU baseline runs on")
     ap.add_argument("--cpu-repeats", type=int, default=3)
+    ap.add_argument("--gather", default="push", choices=["push", "nccl"],
+                    help="reassembly of y/C at N > 1: peer-store push kernel (default) or NCCL all-gather")
     ap.add_argument("--no-check", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()

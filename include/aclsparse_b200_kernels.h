@@ -89,6 +89,13 @@ void spmm_b200_kernel_do(const void* colInd, const void* values, const void* b, 
 void aclsp_b200_row_block_bounds_kernel_do(const void* rowPtr, uint32_t rows, uint32_t nnz, int32_t indexBase,
                                            uint32_t parts, void* bounds, void* stream);
 
+/* Copies `countElems` floats at element `offsetElems` of `src` to the same place in each of the
+ * `numPeers` (at most 16) buffers of the host array `peers` - peer-mapped device pointers of the other
+ * ranks' result buffers - with plain stores, all peers in one launch.  The caller supplies the barrier
+ * that follows.  No counterpart in the reference, which is single-device. */
+void aclsp_b200_push_slice_kernel_do(const void* src, void* const* peers, uint32_t numPeers, int64_t offsetElems,
+                                     int64_t countElems, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

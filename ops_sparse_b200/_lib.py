@@ -134,9 +134,10 @@ SIGNATURES = {
     "spmm_b200_preprocess_kernel_do": [_P, _P, c_uint32, c_uint32, c_uint32, c_uint32, c_int32, _P],
     "spmm_b200_kernel_do": [_P, _P, _P, _P, _P, POINTER(SpmmParams), _P],
     "aclsp_b200_row_block_bounds_kernel_do": [_P, c_uint32, c_uint32, c_int32, c_uint32, _P, _P],
+    "aclsp_b200_push_slice_kernel_do": [_P, POINTER(c_void_p), c_uint32, c_int64, c_int64, _P],
 }
 _VOID = {"spmv_b200_preprocess_kernel_do", "spmv_b200_kernel_do", "spmm_b200_preprocess_kernel_do",
-         "spmm_b200_kernel_do", "aclsp_b200_row_block_bounds_kernel_do"}
+         "spmm_b200_kernel_do", "aclsp_b200_row_block_bounds_kernel_do", "aclsp_b200_push_slice_kernel_do"}
 
 _lib = None
 

@@ -1,0 +1,74 @@
+/*
+ * Reassembly of y / C across the GPUs of one node by peer stores.
+ *
+ * Each rank owns a contiguous block of rows of the result.  After its product
+ * it writes that block into the result buffer of every other rank through
+ * peer-mapped pointers (plain 128-bit stores over NVLink / NVSwitch): one
+ * launch, all peers at once, no staging copy and no collective library call.
+ * Ranks then meet at a barrier of the caller's choosing.  No TMA, no multicast
+ * load: every access to a peer's memory here is an ordinary store.
+ *
+ * The reference library is single-device; this file has no counterpart there.
+ */
+#include <cstdint>
+
+#include <cuda_runtime.h>
+
+#include "aclsparse_b200_kernels.h"
+
+namespace {
+
+constexpr int kMaxPeers = 16;
+
+struct PeerList {
+    float* ptr[kMaxPeers];
+};
+
+// grid.y selects the peer; the block of `count` floats at element `offset` is
+// copied from `src` (this rank's buffer) to the same place in the peer's buffer.
+__global__ void PushSliceKernel(const float* __restrict__ src, PeerList peers, int64_t offset, int64_t count)
+{
+    float* __restrict__ dst = peers.ptr[blockIdx.y] + offset;
+    const float* __restrict__ from = src + offset;
+    // Both sides sit at the same offset of equally aligned buffers, so one
+    // prologue brings both to a 16-byte boundary.
+    const int64_t mis = (reinterpret_cast<uintptr_t>(from) & 15u) / 4u;
+    int64_t head = mis == 0 ? 0 : 4 - mis;
+    head = head < count ? head : count;
+    const int64_t vecs = (count - head) / 4;
+    const int64_t tid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    const int64_t step = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    if (tid < head) {
+        dst[tid] = from[tid];
+    }
+    const float4* from4 = reinterpret_cast<const float4*>(from + head);
+    float4* dst4 = reinterpret_cast<float4*>(dst + head);
+    for (int64_t v = tid; v < vecs; v += step) {
+        dst4[v] = from4[v];
+    }
+    const int64_t tail = head + 4 * vecs;
+    if (tid < count - tail) {
+        dst[tail + tid] = from[tail + tid];
+    }
+}
+
+}  // namespace
+
+extern "C" void aclsp_b200_push_slice_kernel_do(const void* src, void* const* peers, uint32_t numPeers,
+                                                int64_t offsetElems, int64_t countElems, void* stream)
+{
+    if (numPeers == 0 || countElems <= 0) {
+        return;
+    }
+    PeerList list{};
+    const uint32_t n = numPeers > kMaxPeers ? kMaxPeers : numPeers;
+    for (uint32_t i = 0; i < n; ++i) {
+        list.ptr[i] = static_cast<float*>(peers[i]);
+    }
+    // Enough blocks to keep the links busy, few enough to launch quickly.
+    int64_t blocks = (countElems / 4 + 255) / 256;
+    blocks = blocks < 1 ? 1 : (blocks > 592 / static_cast<int64_t>(n) + 1 ? 592 / static_cast<int64_t>(n) + 1 : blocks);
+    const dim3 grid(static_cast<unsigned>(blocks), n);
+    PushSliceKernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const float*>(src), list,
+                                                                        offsetElems, countElems);
+}

@@ -14,8 +14,9 @@
  *   2. rows that end inside the tile are reduced by groups of 2^class lanes
  *      ("vector per row", class picked per tile by the preprocessing pass from
  *      the tile's mean row length; class 5 is warp per row) with a shuffle
- *      tree; row pieces of kLongSegment products or more are reduced by the
- *      whole CTA instead;
+ *      tree; pieces of kWarpSegment products or more that are too long for their
+ *      lanes get a whole warp each (warp per row), pieces of kLongSegment or
+ *      more the whole CTA;
  *   3. the piece of a row that continues into the next tile becomes the tile's
  *      carry-out, and the piece of a row that began in an earlier tile becomes
  *      its head partial; a second small kernel adds the carries of a split row
@@ -46,7 +47,9 @@ namespace {
 constexpr int kThreads = 256;
 constexpr int kWarps = kThreads / 32;
 constexpr int kTile = ACLSP_SPMV_TILE_ITEMS;
-constexpr int kLongSegment = 256;
+constexpr int kWarpSegment = 64;    // pieces at least this long get a whole warp
+constexpr int kLongSegment = 1024;  // pieces at least this long get the whole CTA
+constexpr int kMaxWarpSeg = kTile / kWarpSegment;
 constexpr int kMaxLong = kTile / kLongSegment;
 
 struct SpmvPlanView {
@@ -130,7 +133,9 @@ SpmvTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ val
     __shared__ __align__(16) float sPool[2 * kTile + 24];
     __shared__ double sWarp[kWarps];
     __shared__ int sLong[kMaxLong];
+    __shared__ int sWarpSeg[kMaxWarpSeg];
     __shared__ int sNumLong;
+    __shared__ int sNumWarpSeg;
 
     const int tid = threadIdx.x;
     const int t = blockIdx.x;
@@ -165,6 +170,7 @@ SpmvTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ val
     int* sOff = reinterpret_cast<int*>(sPool + 2 * kTile + 24) - (nr + 2);
     if (tid == 0) {
         sNumLong = 0;
+        sNumWarpSeg = 0;
     }
     for (int k = tid; k <= nr; k += kThreads) {
         sOff[k] = ClampOffset(plan.rowPtr[i0 + k], nnz) - j0;
@@ -205,24 +211,23 @@ SpmvTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ val
             *reinterpret_cast<float4*>(sHi + 4 * v) = hi;
             *reinterpret_cast<float4*>(sLo + 4 * v) = lo;
         };
-        // A tile spans at most kTile / 4 + 1 vectors: two per thread, both
-        // loads in flight before either is used, plus a one-vector remainder.
-        Vec4 va, vb;
-        const bool hasA = tid < nvec;
-        const bool hasB = tid + kThreads < nvec;
-        if (hasA) {
-            loadVec(tid, va);
+        // A tile spans at most kTile / 4 + 1 vectors: kVecsPerThread per thread,
+        // all of them loaded before the first is used, plus a one-vector remainder.
+        constexpr int kVecsPerThread = kTile / 4 / kThreads;
+        Vec4 vv[kVecsPerThread];
+#pragma unroll
+        for (int u = 0; u < kVecsPerThread; ++u) {
+            if (tid + u * kThreads < nvec) {
+                loadVec(tid + u * kThreads, vv[u]);
+            }
         }
-        if (hasB) {
-            loadVec(tid + kThreads, vb);
+#pragma unroll
+        for (int u = 0; u < kVecsPerThread; ++u) {
+            if (tid + u * kThreads < nvec) {
+                useVec(tid + u * kThreads, vv[u]);
+            }
         }
-        if (hasA) {
-            useVec(tid, va);
-        }
-        if (hasB) {
-            useVec(tid + kThreads, vb);
-        }
-        for (int v = tid + 2 * kThreads; v < nvec; v += kThreads) {
+        for (int v = tid + kVecsPerThread * kThreads; v < nvec; v += kThreads) {
             Vec4 vc;
             loadVec(v, vc);
             useVec(v, vc);
@@ -262,13 +267,20 @@ SpmvTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ val
     // Sum of products [b, e) taken by this thread with the given stride: the hi
     // parts in fp64, the (tiny) lo parts in fp32, joined at the end.
     auto strided = [&](int b, int e, int first, int stride) {
-        double hi = 0.0;
-        float lo = 0.0f;
-        for (int q = b + first; q < e; q += stride) {
-            hi += static_cast<double>(hiT[q]);
-            lo += loT[q];
+        double h0 = 0.0, h1 = 0.0;
+        float l0 = 0.0f, l1 = 0.0f;
+        int q = b + first;
+        for (; q + stride < e; q += 2 * stride) {  // two independent chains
+            h0 += static_cast<double>(hiT[q]);
+            l0 += loT[q];
+            h1 += static_cast<double>(hiT[q + stride]);
+            l1 += loT[q + stride];
         }
-        return hi + static_cast<double>(lo);
+        if (q < e) {
+            h0 += static_cast<double>(hiT[q]);
+            l0 += loT[q];
+        }
+        return (h0 + h1) + static_cast<double>(l0 + l1);
     };
 
     // Vector per row: 2^cls lanes share a row piece.
@@ -285,13 +297,22 @@ SpmvTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ val
         if (active) {
             const int b = segBegin(k);
             const int e = segEnd(k);
-            if (e - b >= kLongSegment) {
+            const int len = e - b;
+            if (len >= kWarpSegment && len >= 32 * lanes) {
+                // Too long for its lanes: queue it for a warp, or for the whole CTA.
+                // A valid CSR fills neither list beyond its capacity; row offsets
+                // that overlap could, and the excess is dropped.
                 if (lane == 0) {
-                    // A valid CSR has at most kMaxLong such pieces per tile; row
-                    // offsets that overlap could claim more, those are dropped.
-                    const int slot = atomicAdd(&sNumLong, 1);
-                    if (slot < kMaxLong) {
-                        sLong[slot] = k;
+                    if (len >= kLongSegment) {
+                        const int slot = atomicAdd(&sNumLong, 1);
+                        if (slot < kMaxLong) {
+                            sLong[slot] = k;
+                        }
+                    } else {
+                        const int slot = atomicAdd(&sNumWarpSeg, 1);
+                        if (slot < kMaxWarpSeg) {
+                            sWarpSeg[slot] = k;
+                        }
                     }
                 }
                 active = false;
@@ -308,6 +329,19 @@ SpmvTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ val
         }
     }
     __syncthreads();
+
+    // Medium pieces: warp per row.
+    const int numWarpSeg = sNumWarpSeg < kMaxWarpSeg ? sNumWarpSeg : kMaxWarpSeg;
+    for (int q = tid >> 5; q < numWarpSeg; q += kWarps) {
+        const int k = sWarpSeg[q];
+        double sum = strided(segBegin(k), segEnd(k), tid & 31, 32);
+        for (int o = 16; o > 0; o >>= 1) {
+            sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        }
+        if ((tid & 31) == 0) {
+            emit(k, sum);
+        }
+    }
 
     // Long pieces: the whole CTA adds one piece, warps combined in warp order.
     const int numLong = sNumLong < kMaxLong ? sNumLong : kMaxLong;

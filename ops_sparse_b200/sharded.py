@@ -8,12 +8,22 @@ into ``world_size`` contiguous row blocks that balance the non-zeros:
 Rank g holds rows [bounds[g], bounds[g+1]) of A (row offsets rebased to start at
 0, its slice of the column indices and values), a full replica of x or B, and
 computes its slice of y or C with the single-GPU operators.  The only exchange
-is the all-gather that reassembles y / C on every rank; row blocks have unequal
-row counts, so slices travel padded to the largest block and are compacted by
-one concatenation afterwards.  The reference library is single-device; this
-layer has no counterpart there.
+is the reassembly of y / C on every rank, in one of two ways:
+
+* ``push`` (default on GPUs): the result lives in a symmetric-memory buffer that
+  every rank maps; a rank's product writes its row block in place, one kernel of
+  this library (``aclsp_b200_push_slice_kernel_do``) stores that block into all
+  peers' buffers over NVLink, and a device-side barrier closes the step.  No
+  padding, no concatenation, no collective-library call on the data path.
+* ``nccl``: an all-gather; row blocks have unequal row counts, so slices travel
+  padded to the largest block and are compacted by one concatenation afterwards.
+
+The reference library is single-device; this layer has no counterpart there.
 """
 from __future__ import annotations
+
+import ctypes
+import os
 
 import numpy as np
 import torch
@@ -58,6 +68,53 @@ class _Gather:
         return torch.cat([self.slots[g][: int(self.rows[g])] for g in range(self.world)])
 
 
+class _PushGather:
+    """Reassembly by peer stores into a symmetric-memory result buffer (see the module docstring).
+
+    The buffer of step k is overwritten by the peers' pushes of step k+1: a consumer that still reads
+    it then must copy it first, exactly as with a reused all-gather output.
+    """
+
+    def __init__(self, bounds: np.ndarray, rank: int, width: int, device, group=None):
+        import torch.distributed._symmetric_memory as symm
+        # Only plain peer stores are used here; keep the buffer off NVLink multicast objects.
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        self.rank, self.width = rank, width
+        self.world = bounds.size - 1
+        group = group if group is not None else dist.group.WORLD
+        total = int(bounds[-1])
+        shape = (max(total, 1), width) if width > 1 else (max(total, 1),)
+        self.full = symm.empty(shape, dtype=torch.float32, device=device)
+        self.full.zero_()
+        self.handle = symm.rendezvous(self.full, group=group)
+        r0, r1 = int(bounds[rank]), int(bounds[rank + 1])
+        self.local = self.full[r0:r1]
+        self.offset, self.count = r0 * width, (r1 - r0) * width
+        ptrs = [int(p) for g, p in enumerate(self.handle.buffer_ptrs) if g != rank]
+        self.peers = (ctypes.c_void_p * max(len(ptrs), 1))(*ptrs)
+        self.num_peers = len(ptrs)
+        self._lib = L.lib()
+
+    def run(self) -> torch.Tensor:
+        stream = torch.cuda.current_stream().cuda_stream or 0x1
+        self._lib.aclsp_b200_push_slice_kernel_do(self.full.data_ptr(), self.peers, self.num_peers, self.offset,
+                                                  self.count, stream)
+        self.handle.barrier()
+        return self.full
+
+
+def _make_gather(mode: str, bounds, rank, width, device, group):
+    """``push`` where symmetric memory can be set up, else the all-gather; returns (gather, mode used)."""
+    world = bounds.size - 1
+    if mode == "push" and world > 1 and torch.device(device).type == "cuda":
+        try:
+            return _PushGather(bounds, rank, width, device, group), "push"
+        except Exception as err:  # symmetric memory is optional plumbing; the all-gather gives the same result
+            import warnings
+            warnings.warn(f"symmetric-memory push unavailable ({err!r}); using the NCCL all-gather")
+    return _Gather(bounds, rank, width, device, group), "nccl"
+
+
 class ShardedSpMV:
     """y = alpha * A * x + beta * y with A row-block sharded over the ranks of ``group``.
 
@@ -66,14 +123,14 @@ class ShardedSpMV:
     partition / gather logic without a GPU; there is no CPU implementation in this package.)
     """
 
-    def __init__(self, cfg: dict, rank: int, world: int, device, group=None, local_product=None):
+    def __init__(self, cfg: dict, rank: int, world: int, device, group=None, local_product=None, gather="push"):
         self.rank, self.world, self.device = rank, world, device
         base = cfg.get("index_base", 0)
         self.bounds = row_block_bounds_host(cfg["row_ptr"], cfg["nnz"], world, base)
         self.local_ptr, self.local_col, self.local_val = shard_csr(cfg["row_ptr"], cfg["col_ind"], cfg["values"],
                                                                    self.bounds, rank, base)
         self.r0, self.r1 = int(self.bounds[rank]), int(self.bounds[rank + 1])
-        self.gather = _Gather(self.bounds, rank, 1, device, group)
+        self.gather, self.gather_mode = _make_gather(gather, self.bounds, rank, 1, device, group)
         self.x = torch.from_numpy(cfg["x"]).to(device)
         self.y_local = self.gather.local
         self.y_local.copy_(torch.from_numpy(cfg["y"][self.r0:self.r1]).to(device))
@@ -103,7 +160,7 @@ class ShardedSpMV:
 class ShardedSpMM:
     """C = alpha * A * B + beta * C (row-major B and C) with A row-block sharded over the ranks."""
 
-    def __init__(self, cfg: dict, rank: int, world: int, device, group=None, local_product=None):
+    def __init__(self, cfg: dict, rank: int, world: int, device, group=None, local_product=None, gather="push"):
         self.rank, self.world, self.device = rank, world, device
         base = cfg.get("index_base", 0)
         n = cfg["n"]
@@ -111,7 +168,7 @@ class ShardedSpMM:
         self.local_ptr, self.local_col, self.local_val = shard_csr(cfg["row_ptr"], cfg["col_ind"], cfg["values"],
                                                                    self.bounds, rank, base)
         self.r0, self.r1 = int(self.bounds[rank]), int(self.bounds[rank + 1])
-        self.gather = _Gather(self.bounds, rank, n, device, group)
+        self.gather, self.gather_mode = _make_gather(gather, self.bounds, rank, n, device, group)
         self.b = torch.from_numpy(cfg["b"]).to(device)
         self.c_local = self.gather.local
         self.c_local.copy_(torch.from_numpy(cfg["c"][self.r0:self.r1]).to(device))
@@ -140,7 +197,6 @@ class ShardedSpMM:
 
 def init_process_group_from_env(backend: "str | None" = None):
     """RANK / LOCAL_RANK / WORLD_SIZE / MASTER_* from the environment (torchrun); returns (rank, world, device)."""
-    import os
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
