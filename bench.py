@@ -229,6 +229,7 @@ def run_ours(args, cfg):
         check = {"rows_checked": rows, "violations": bad, "max_abs_err": max_abs, "max_rel_err": max_rel,
                  "rtol": 1e-5, "atol": 1e-6}
     del full
+    graphed = (not args.no_graph) and op.capture(alpha, beta)
 
     # ---- device-resident steps
     # nvidia-smi needs about a second to deliver its first sample, far longer than a few steps take:
@@ -316,7 +317,8 @@ def run_ours(args, cfg):
         "scaling": "strong", "vs_baseline": None, "dtype": "f32 data, f64 accumulate" if spmv else "f32",
         "data": "synthetic",
         "config": {"workload": describe(cfg), "sharding": f"row blocks by nnz over {world} GPU(s), x/B replicated, "
-                   f"reassembly of y/C inside the step ({op.gather_mode if world > 1 else 'none at 1 GPU'})", "l2": "inputs larger than L2 (matrix streamed from HBM every "
+                   f"reassembly of y/C inside the step ({op.gather_mode if world > 1 else 'none at 1 GPU'})",
+                   "launch": "one CUDA graph replay per step" if graphed else "kernel by kernel", "l2": "inputs larger than L2 (matrix streamed from HBM every "
                    "step); no flush", "per_step_ms_min_median_max": [float(np.min(per_step)),
                                                                      float(np.median(per_step)),
                                                                      float(np.max(per_step))]},
@@ -356,8 +358,11 @@ def main():
     ap.add_argument("--check-rows", type=int, default=1 << 20, help="rows compared with the oracle before timing")
     ap.add_argument("--cpu-rows", type=int, default=1 << 22, help="row block the CPU baseline runs on")
     ap.add_argument("--cpu-repeats", type=int, default=3)
-    ap.add_argument("--gather", default="push", choices=["push", "nccl"],
-                    help="reassembly of y/C at N > 1: peer-store push kernel (default) or NCCL all-gather")
+    ap.add_argument("--gather", default="fused", choices=["fused", "push", "nccl"],
+                    help="reassembly of y/C at N > 1: mirror stores inside the product kernels (default), "
+                    "a separate peer-store kernel, or the NCCL all-gather")
+    ap.add_argument("--no-graph", action="store_true", help="launch every step kernel by kernel instead of "
+                    "replaying the step as one CUDA graph")
     ap.add_argument("--no-check", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()

@@ -39,6 +39,17 @@ aclsparseStatus_t aclsparseB200SpMVNoAlloc(aclrtStream stream, int64_t rows, int
                                            aclsparseIndexBase_t idxBase, const float* x, float* y, float alpha,
                                            float beta);
 
+/* Mirrors of an output vector / matrix: after this call every element that aclsparseSpMV (aclsparseSpMM)
+ * writes to `vec` (`mat`) is also stored at the same element position of each of the `count` (at most 7)
+ * buffers `mirrors[0..count)`, by the product kernels themselves.  With the result buffers of the other
+ * GPUs of the node as mirrors (peer-mapped pointers, each advanced to this device's row block) the product
+ * and the reassembly of a row-block-sharded y / C over NVLink become one kernel; the caller follows it with
+ * a barrier across the devices.  A mirror has the layout (stride, leading dimension, order) of the vector
+ * or matrix itself.  count == 0 clears the list.  The host array `mirrors` is copied.  beta scales the
+ * values of `vec` / `mat` only; mirrors are never read.  No counterpart in the reference. */
+aclsparseStatus_t aclsparseB200DnVecSetMirrors(aclsparseDnVecDescr_t vec, int count, void* const* mirrors);
+aclsparseStatus_t aclsparseB200DnMatSetMirrors(aclsparseDnMatDescr_t mat, int count, void* const* mirrors);
+
 #ifdef __cplusplus
 }
 #endif

@@ -19,6 +19,14 @@
 extern "C" {
 #endif
 
+/* Mirrors of an output: besides the result buffer itself a kernel can store every element it writes at the
+ * same element position of up to ACLSP_MAX_MIRRORS further buffers - the result buffers of the other GPUs
+ * of the node, mapped into this device's address space - so that the product and the reassembly of the
+ * sharded result over NVLink are one kernel.  mirrorDelta[m] is the BYTE distance from the output base to
+ * mirror m's base.  Plain stores only; the caller's barrier follows the launch.  The reference library is
+ * single-device and has nothing of the kind. */
+#define ACLSP_MAX_MIRRORS 7
+
 /* Per-launch parameters of the SpMV kernels.  Counterpart of the reference's
  * SpmvArch35TilingData (sparse/spmv/arch35/spmv_tiling_data.h:38-68), passed
  * by value as a kernel argument instead of being published to the workspace. */
@@ -35,6 +43,9 @@ typedef struct AclspSpmvParams {
     float beta;
     const float* alphaPtr;   /* device pointer mode: scalars are read on the device */
     const float* betaPtr;
+    uint32_t numMirrors;     /* 0: y only */
+    uint32_t reserved;
+    int64_t mirrorDelta[ACLSP_MAX_MIRRORS];
 } AclspSpmvParams;
 
 /* Per-launch parameters of the SpMM kernels.  Counterpart of the reference's
@@ -56,6 +67,9 @@ typedef struct AclspSpmmParams {
     float beta;
     const float* alphaPtr;
     const float* betaPtr;
+    uint32_t numMirrors;     /* 0: C only */
+    uint32_t reserved2;
+    int64_t mirrorDelta[ACLSP_MAX_MIRRORS];
 } AclspSpmmParams;
 
 /* Builds the SpMV plan in `workspace`: header, base-0 row offsets, merge-path

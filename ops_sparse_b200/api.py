@@ -117,6 +117,11 @@ class DnVec:
         self.values = values
         check("aclsparseDnVecSetValues", L.lib().aclsparseDnVecSetValues(self._d, _ptr(values)))
 
+    def set_mirrors(self, pointers) -> None:
+        """Device addresses (ints) of buffers that receive every element SpMV writes to this vector."""
+        arr = (c_void_p * max(len(pointers), 1))(*[int(p) for p in pointers])
+        check("aclsparseB200DnVecSetMirrors", L.lib().aclsparseB200DnVecSetMirrors(self._d, len(pointers), arr))
+
     def close(self) -> None:
         if self._d:
             L.lib().aclsparseDestroyDnVec(self._d)
@@ -143,6 +148,11 @@ class DnMat:
     def set_values(self, values) -> None:
         self.values = values
         check("aclsparseDnMatSetValues", L.lib().aclsparseDnMatSetValues(self._d, _ptr(values)))
+
+    def set_mirrors(self, pointers) -> None:
+        """Device addresses (ints) of buffers that receive every element SpMM writes to this matrix."""
+        arr = (c_void_p * max(len(pointers), 1))(*[int(p) for p in pointers])
+        check("aclsparseB200DnMatSetMirrors", L.lib().aclsparseB200DnMatSetMirrors(self._d, len(pointers), arr))
 
     def close(self) -> None:
         if self._d:

@@ -36,3 +36,36 @@ extern "C" aclsparseStatus_t aclsparseB200RowBlockBounds(aclsparseHandle_t handl
     }
     return ACL_SPARSE_STATUS_SUCCESS;
 }
+
+namespace {
+
+template <typename Descr>
+aclsparseStatus_t SetMirrors(Descr* d, uint32_t signature, int count, void* const* mirrors)
+{
+    if (d == nullptr || d->signature != signature || count < 0 || count > ACLSP_MAX_MIRRORS ||
+        (count > 0 && mirrors == nullptr)) {
+        return ACL_SPARSE_STATUS_INVALID_VALUE;
+    }
+    for (int m = 0; m < count; ++m) {
+        if (mirrors[m] == nullptr) {
+            return ACL_SPARSE_STATUS_INVALID_VALUE;
+        }
+    }
+    d->numMirrors = count;
+    for (int m = 0; m < ACLSP_MAX_MIRRORS; ++m) {
+        d->mirrors[m] = m < count ? mirrors[m] : nullptr;
+    }
+    return ACL_SPARSE_STATUS_SUCCESS;
+}
+
+}  // namespace
+
+extern "C" aclsparseStatus_t aclsparseB200DnVecSetMirrors(aclsparseDnVecDescr_t vec, int count, void* const* mirrors)
+{
+    return SetMirrors(vec, kDnVecSignature, count, mirrors);
+}
+
+extern "C" aclsparseStatus_t aclsparseB200DnMatSetMirrors(aclsparseDnMatDescr_t mat, int count, void* const* mirrors)
+{
+    return SetMirrors(mat, kDnMatSignature, count, mirrors);
+}

@@ -118,6 +118,9 @@ struct aclsparseDnVecDescr {
     void* values = nullptr;
     int64_t stride = 1;
     aclDataType valueType = ACL_FLOAT;
+    // aclsparseB200DnVecSetMirrors: further buffers that receive every element SpMV writes.
+    int numMirrors = 0;
+    void* mirrors[7] = {};
 };
 
 struct aclsparseDnMatDescr {
@@ -130,6 +133,9 @@ struct aclsparseDnMatDescr {
     aclDataType valueType = ACL_FLOAT;
     int32_t batchCount = 1;
     int64_t batchStride = 0;
+    // aclsparseB200DnMatSetMirrors: further buffers that receive every element SpMM writes.
+    int numMirrors = 0;
+    void* mirrors[7] = {};
 };
 
 uint64_t AclspNextWorkspaceOwnerId();

@@ -293,6 +293,14 @@ extern "C" aclsparseStatus_t aclsparseSpMM(aclsparseHandle_t handle, aclsparseOp
         params.alpha = *static_cast<const float*>(alpha);
         params.beta = *static_cast<const float*>(beta);
     }
+    params.numMirrors = static_cast<uint32_t>(matC->numMirrors);
+    for (int m = 0; m < matC->numMirrors; ++m) {
+        params.mirrorDelta[m] = static_cast<const char*>(matC->mirrors[m]) - static_cast<const char*>(matC->values);
+        if (params.mirrorDelta[m] % 4 != 0) {
+            ACLSP_LOGE(kApi, "mirror %d is not aligned like the output", m);
+            return ACL_SPARSE_STATUS_INVALID_VALUE;
+        }
+    }
 
     (void)cudaGetLastError();
     spmm_b200_kernel_do(a->idxs, a->values, matB->values, matC->values, buffer, &params, handle->stream);

@@ -315,6 +315,11 @@ SpmmTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ val
                 }
             }
             *reinterpret_cast<V*>(dst) = out;
+            // Mirrors of C (the other GPUs' result buffers when the matrix is
+            // sharded) receive the same 32 * VW contiguous floats per warp.
+            for (uint32_t m = 0; m < p.numMirrors; ++m) {
+                *reinterpret_cast<V*>(reinterpret_cast<char*>(dst) + p.mirrorDelta[m]) = out;
+            }
         };
         // A finished row goes to C, unless it is the warp's first row and its
         // beginning lies elsewhere: then it waits in shared memory.
@@ -520,7 +525,11 @@ __global__ void SpmmCarryFixupKernel(float* __restrict__ C, SpmmPlanView plan, A
             sum += plan.carry[static_cast<size_t>(2 * t + 1) * n + c];
             float* dst = C + static_cast<int64_t>(i0) * ds.cRow + static_cast<int64_t>(c) * ds.cCol;
             const double r = static_cast<double>(sc.alpha) * sum;
-            *dst = static_cast<float>(sc.betaZero ? r : r + static_cast<double>(sc.beta) * *dst);
+            const float out = static_cast<float>(sc.betaZero ? r : r + static_cast<double>(sc.beta) * *dst);
+            *dst = out;
+            for (uint32_t m = 0; m < p.numMirrors; ++m) {
+                *reinterpret_cast<float*>(reinterpret_cast<char*>(dst) + p.mirrorDelta[m]) = out;
+            }
         }
     }
 }
@@ -583,7 +592,10 @@ extern "C" void spmm_b200_kernel_do(const void* colInd, const void* values, cons
     ds.cCol = p.orderC == 0 ? 1 : p.ldc;
 
     const bool unit = ds.bCol == 1 && ds.cCol == 1;
-    const uintptr_t addr = reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(c);
+    uintptr_t addr = reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(c);
+    for (uint32_t m = 0; m < p.numMirrors && m < ACLSP_MAX_MIRRORS; ++m) {
+        addr |= static_cast<uintptr_t>(p.mirrorDelta[m]);  // a mirror is as aligned as C and its distance from C
+    }
     int vw = 1;
     if (unit && p.n % 4 == 0 && p.n >= 128 && p.ldb % 4 == 0 && p.ldc % 4 == 0 && addr % 16 == 0) {
         vw = 4;

@@ -406,6 +406,14 @@ extern "C" aclsparseStatus_t aclsparseSpMV(aclsparseHandle_t handle, aclsparseOp
         params.alpha = *static_cast<const float*>(alpha);
         params.beta = *static_cast<const float*>(beta);
     }
+    params.numMirrors = static_cast<uint32_t>(vecY->numMirrors);
+    for (int m = 0; m < vecY->numMirrors; ++m) {
+        params.mirrorDelta[m] = static_cast<const char*>(vecY->mirrors[m]) - static_cast<const char*>(vecY->values);
+        if (params.mirrorDelta[m] % 4 != 0) {
+            ACLSP_LOGE(kApi, "mirror %d is not aligned like the output", m);
+            return ACL_SPARSE_STATUS_INVALID_VALUE;
+        }
+    }
 
     (void)cudaGetLastError();
     spmv_b200_kernel_do(mat->idxs, mat->values, vecX->values, vecY->values, externalBuffer, &params,

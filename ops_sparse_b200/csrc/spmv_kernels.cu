@@ -98,11 +98,19 @@ __device__ __forceinline__ Scalars LoadScalars(const AclspSpmvParams& p)
     return s;
 }
 
-// beta == 0 must not read y: it may hold NaN or be uninitialised.
-__device__ __forceinline__ void StoreRow(float* __restrict__ y, int64_t index, double sum, const Scalars& s)
+// beta == 0 must not read y: it may hold NaN or be uninitialised.  The value
+// also goes to the same element of every mirror of y (the other GPUs' result
+// buffers when the matrix is sharded): plain stores, never read back.
+__device__ __forceinline__ void StoreRow(float* __restrict__ y, int64_t index, double sum, const Scalars& s,
+                                         const AclspSpmvParams& p)
 {
     const double r = s.betaZero ? s.alpha * sum : s.alpha * sum + s.beta * static_cast<double>(y[index]);
-    y[index] = static_cast<float>(r);
+    const float out = static_cast<float>(r);
+    float* dst = y + index;
+    *dst = out;
+    for (uint32_t m = 0; m < p.numMirrors; ++m) {
+        *reinterpret_cast<float*>(reinterpret_cast<char*>(dst) + p.mirrorDelta[m]) = out;
+    }
 }
 
 // One product as an unevaluated sum hi + lo of two floats: hi is the rounded
@@ -261,7 +269,7 @@ SpmvTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ val
         } else if (k == 0 && headOpen) {
             plan.carry[2 * t + 1] = sum;
         } else {
-            StoreRow(y, static_cast<int64_t>(i0 + k) * p.yStride, sum, sc);
+            StoreRow(y, static_cast<int64_t>(i0 + k) * p.yStride, sum, sc, p);
         }
     };
     // Sum of products [b, e) taken by this thread with the given stride: the hi
@@ -398,7 +406,7 @@ __global__ void SpmvCarryFixupKernel(float* __restrict__ y, SpmvPlanView plan, A
         sum += plan.carry[2 * u];
     }
     sum += plan.carry[2 * t + 1];
-    StoreRow(y, static_cast<int64_t>(i0) * p.yStride, sum, LoadScalars(p));
+    StoreRow(y, static_cast<int64_t>(i0) * p.yStride, sum, LoadScalars(p), p);
 }
 
 }  // namespace

@@ -8,13 +8,17 @@ into ``world_size`` contiguous row blocks that balance the non-zeros:
 Rank g holds rows [bounds[g], bounds[g+1]) of A (row offsets rebased to start at
 0, its slice of the column indices and values), a full replica of x or B, and
 computes its slice of y or C with the single-GPU operators.  The only exchange
-is the reassembly of y / C on every rank, in one of two ways:
+is the reassembly of y / C on every rank, in one of three ways:
 
-* ``push`` (default on GPUs): the result lives in a symmetric-memory buffer that
-  every rank maps; a rank's product writes its row block in place, one kernel of
-  this library (``aclsp_b200_push_slice_kernel_do``) stores that block into all
-  peers' buffers over NVLink, and a device-side barrier closes the step.  No
-  padding, no concatenation, no collective-library call on the data path.
+* ``fused`` (default on GPUs): the result lives in a symmetric-memory buffer that
+  every rank maps, and the peers' buffers are registered as mirrors of the local
+  output (``aclsparseB200DnVecSetMirrors`` / ``DnMatSetMirrors``): the product
+  kernels store each finished row into all ranks' buffers themselves, over
+  NVLink, while the rest of the matrix is still being multiplied.  A device-side
+  barrier closes the step.  No padding, no concatenation, no separate transfer.
+* ``push``: same buffers, but the product writes its row block locally and one
+  further kernel (``aclsp_b200_push_slice_kernel_do``) stores the block into all
+  peers' buffers before the barrier.
 * ``nccl``: an all-gather; row blocks have unequal row counts, so slices travel
   padded to the largest block and are compacted by one concatenation afterwards.
 
@@ -63,8 +67,9 @@ class _Gather:
         self.local = self.slots[rank][: int(self.rows[rank])]
 
     def run(self) -> torch.Tensor:
-        if self.world > 1:
-            dist.all_gather_into_tensor(self.slots.view(-1), self.slots[self.rank].reshape(-1), group=self.group)
+        if self.world == 1:
+            return self.local
+        dist.all_gather_into_tensor(self.slots.view(-1), self.slots[self.rank].reshape(-1), group=self.group)
         return torch.cat([self.slots[g][: int(self.rows[g])] for g in range(self.world)])
 
 
@@ -75,7 +80,7 @@ class _PushGather:
     it then must copy it first, exactly as with a reused all-gather output.
     """
 
-    def __init__(self, bounds: np.ndarray, rank: int, width: int, device, group=None):
+    def __init__(self, bounds: np.ndarray, rank: int, width: int, device, group=None, fused=False):
         import torch.distributed._symmetric_memory as symm
         # Only plain peer stores are used here; keep the buffer off NVLink multicast objects.
         os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
@@ -93,29 +98,70 @@ class _PushGather:
         ptrs = [int(p) for g, p in enumerate(self.handle.buffer_ptrs) if g != rank]
         self.peers = (ctypes.c_void_p * max(len(ptrs), 1))(*ptrs)
         self.num_peers = len(ptrs)
+        self.fused = fused
+        # Peers' addresses of this rank's row block: the mirrors of the local output in fused mode.
+        self.mirror_ptrs = [p + self.offset * 4 for p in ptrs]
         self._lib = L.lib()
 
     def run(self) -> torch.Tensor:
-        stream = torch.cuda.current_stream().cuda_stream or 0x1
-        self._lib.aclsp_b200_push_slice_kernel_do(self.full.data_ptr(), self.peers, self.num_peers, self.offset,
-                                                  self.count, stream)
+        if not self.fused:
+            stream = torch.cuda.current_stream().cuda_stream or 0x1
+            self._lib.aclsp_b200_push_slice_kernel_do(self.full.data_ptr(), self.peers, self.num_peers, self.offset,
+                                                      self.count, stream)
         self.handle.barrier()
         return self.full
 
 
 def _make_gather(mode: str, bounds, rank, width, device, group):
-    """``push`` where symmetric memory can be set up, else the all-gather; returns (gather, mode used)."""
+    """``fused`` / ``push`` where symmetric memory can be set up, else the all-gather; returns (gather, mode used)."""
     world = bounds.size - 1
-    if mode == "push" and world > 1 and torch.device(device).type == "cuda":
+    if mode in ("fused", "push") and world > 1 and torch.device(device).type == "cuda":
         try:
-            return _PushGather(bounds, rank, width, device, group), "push"
+            return _PushGather(bounds, rank, width, device, group, fused=mode == "fused"), mode
         except Exception as err:  # symmetric memory is optional plumbing; the all-gather gives the same result
             import warnings
             warnings.warn(f"symmetric-memory push unavailable ({err!r}); using the NCCL all-gather")
     return _Gather(bounds, rank, width, device, group), "nccl"
 
 
-class ShardedSpMV:
+class _GraphedStep:
+    """CUDA-graph replay of one whole step (product kernels, push kernel, barrier).
+
+    At several GPUs a step is a few tens of microseconds of device work behind four launches, which the
+    host cannot issue that fast one by one; replaying them as one graph keeps the step device-bound.
+    Only the symmetric-memory modes are captured (their launches are all plain kernels on one stream).
+    """
+
+    _graph = None
+
+    def capture(self, alpha: float, beta: float) -> bool:
+        """Records ``step(alpha, beta)`` into a graph that later ``step`` calls with the same scalars replay."""
+        if self._product is not None or (self.world > 1 and self.gather_mode == "nccl"):
+            return False
+        side = torch.cuda.Stream(device=self.device)
+        side.wait_stream(torch.cuda.current_stream())
+        self.handle.set_stream(side.cuda_stream)
+        try:
+            with torch.cuda.stream(side):
+                self._eager_step(alpha, beta)  # first use on this stream: nothing lazy is left for the capture
+            side.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                self._eager_step(alpha, beta)
+        finally:
+            self.handle.set_stream(torch.cuda.current_stream().cuda_stream)
+        self._graph = (graph, float(alpha), float(beta))
+        return True
+
+    def step(self, alpha: float, beta: float) -> torch.Tensor:
+        """One product: local row block, then the reassembly; returns the full result (identical on every rank)."""
+        if self._graph is not None and self._graph[1:] == (float(alpha), float(beta)):
+            self._graph[0].replay()
+            return self.gather.full if self.world > 1 else self.gather.local
+        return self._eager_step(alpha, beta)
+
+
+class ShardedSpMV(_GraphedStep):
     """y = alpha * A * x + beta * y with A row-block sharded over the ranks of ``group``.
 
     ``local_product(local_csr, x, y_local, alpha, beta)`` computes one rank's slice; by default it is
@@ -123,7 +169,7 @@ class ShardedSpMV:
     partition / gather logic without a GPU; there is no CPU implementation in this package.)
     """
 
-    def __init__(self, cfg: dict, rank: int, world: int, device, group=None, local_product=None, gather="push"):
+    def __init__(self, cfg: dict, rank: int, world: int, device, group=None, local_product=None, gather="fused"):
         self.rank, self.world, self.device = rank, world, device
         base = cfg.get("index_base", 0)
         self.bounds = row_block_bounds_host(cfg["row_ptr"], cfg["nnz"], world, base)
@@ -145,11 +191,12 @@ class ShardedSpMV:
                                      nnz=int(self.local_col.size))
             self.op = api.SpMV(self.handle, self.mat, api.DnVec(self.x), api.DnVec(self.y_local,
                                                                                    size=self.r1 - self.r0))
+            if self.gather_mode == "fused":
+                self.op.y.set_mirrors(self.gather.mirror_ptrs)
             if self.r1 > self.r0:
                 self.op.preprocess()
 
-    def step(self, alpha: float, beta: float) -> torch.Tensor:
-        """One product: local slice, then the all-gather; returns the full y (identical on every rank)."""
+    def _eager_step(self, alpha: float, beta: float) -> torch.Tensor:
         if self._product is not None:
             self._product((self.local_ptr, self.local_col, self.local_val), self.x, self.y_local, alpha, beta)
         elif self.r1 > self.r0:
@@ -157,10 +204,10 @@ class ShardedSpMV:
         return self.gather.run()
 
 
-class ShardedSpMM:
+class ShardedSpMM(_GraphedStep):
     """C = alpha * A * B + beta * C (row-major B and C) with A row-block sharded over the ranks."""
 
-    def __init__(self, cfg: dict, rank: int, world: int, device, group=None, local_product=None, gather="push"):
+    def __init__(self, cfg: dict, rank: int, world: int, device, group=None, local_product=None, gather="fused"):
         self.rank, self.world, self.device = rank, world, device
         base = cfg.get("index_base", 0)
         n = cfg["n"]
@@ -185,9 +232,11 @@ class ShardedSpMM:
             if rows > 0:
                 self.op = api.SpMM(self.handle, self.mat, api.DnMat(cfg["cols"], n, n, self.b),
                                    api.DnMat(rows, n, n, self.c_local))
+                if self.gather_mode == "fused":
+                    self.op.c.set_mirrors(self.gather.mirror_ptrs)
                 self.op.preprocess()
 
-    def step(self, alpha: float, beta: float) -> torch.Tensor:
+    def _eager_step(self, alpha: float, beta: float) -> torch.Tensor:
         if self._product is not None:
             self._product((self.local_ptr, self.local_col, self.local_val), self.b, self.c_local, alpha, beta)
         elif self.r1 > self.r0:

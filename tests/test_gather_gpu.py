@@ -29,3 +29,73 @@ def test_push_slice_copies_exactly_the_block(offset, count, peers):
     for d in dst:
         assert torch.equal(d[offset:offset + count], src[offset:offset + count])
         assert bool((d[:offset] == -1.0).all()) and bool((d[offset + count:] == -1.0).all())
+
+
+@pytest.mark.parametrize("name", ["c1", "c4"])
+def test_graph_replay_of_a_step_equals_the_eager_step(name):
+    """One rank: the step captured as a CUDA graph gives the bits of the kernel-by-kernel step."""
+    from ops_sparse_b200 import sharded, workloads
+    cfg = workloads.make(name, rows=8192 if name == "c4" else None)
+    op_cls = sharded.ShardedSpMV if cfg["kind"] == "spmv" else sharded.ShardedSpMM
+    op = op_cls(cfg, 0, 1, torch.device("cuda:0"))
+    local = op.y_local if cfg["kind"] == "spmv" else op.c_local
+    start = local.clone()
+    eager = op.step(1.25, 0.5).clone()
+    assert op.capture(1.25, 0.5)
+    for _ in range(2):
+        local.copy_(start)
+        replayed = op.step(1.25, 0.5)
+        torch.cuda.synchronize()
+        assert torch.equal(replayed, eager)
+    local.copy_(start)
+    assert torch.equal(op.step(1.0, 0.0), op.step(1.0, 0.0))  # other scalars: eager path, still valid
+
+
+@pytest.mark.parametrize("name,beta", [("c1", 0.0), ("c1", 0.5), ("c3", 0.5), ("c4", 0.0), ("c4", -0.25)])
+@pytest.mark.parametrize("mirrors", [1, 7])
+def test_mirrors_receive_exactly_what_the_output_receives(name, beta, mirrors):
+    """Every element the product writes lands in each mirror too, bit for bit; nothing else is touched."""
+    from ops_sparse_b200 import api, workloads
+    cfg = workloads.make(name, rows={"c1": None, "c3": 40000, "c4": 6000}[name])
+    dev = torch.device("cuda:0")
+    spmv = cfg["kind"] == "spmv"
+    rows, cols = cfg["rows"], cfg["cols"]
+    handle = api.Handle()
+    mat = api.CsrMatrix(rows, cols, torch.from_numpy(cfg["row_ptr"]).to(dev), torch.from_numpy(cfg["col_ind"]).to(dev),
+                        torch.from_numpy(cfg["values"]).to(dev), 0, nnz=cfg["nnz"])
+    out0 = torch.from_numpy(cfg["y"] if spmv else cfg["c"]).to(dev)
+    pad = 5  # guard elements either side of each mirror; also puts the mirrors off 16-byte alignment
+    def run(with_mirrors):
+        out = out0.clone()
+        bufs = [torch.full((out.numel() + 2 * pad,), 7.0, device=dev) for _ in range(mirrors if with_mirrors else 0)]
+        if spmv:
+            y = api.DnVec(out)
+            op = api.SpMV(handle, mat, api.DnVec(torch.from_numpy(cfg["x"]).to(dev)), y)
+            target = y
+        else:
+            n = cfg["n"]
+            c = api.DnMat(rows, n, n, out)
+            op = api.SpMM(handle, mat, api.DnMat(cols, n, n, torch.from_numpy(cfg["b"]).to(dev)), c)
+            target = c
+        if with_mirrors:
+            target.set_mirrors([b.data_ptr() + 4 * pad for b in bufs])
+        op.preprocess()
+        op(1.5, beta)
+        torch.cuda.synchronize()
+        return out, bufs
+    plain, _ = run(False)
+    mirrored, bufs = run(True)
+    assert torch.equal(plain, mirrored)
+    for b in bufs:
+        assert torch.equal(b[pad:-pad], mirrored.reshape(-1))
+        assert bool((b[:pad] == 7.0).all()) and bool((b[-pad:] == 7.0).all())
+
+
+def test_mirror_list_is_validated():
+    from ops_sparse_b200 import api
+    y = api.DnVec(torch.zeros(8, device="cuda"))
+    with pytest.raises(api.AclsparseError):
+        y.set_mirrors([1] * 8)  # more than 7
+    with pytest.raises(api.AclsparseError):
+        y.set_mirrors([0])      # null mirror
+    y.set_mirrors([])           # clears
