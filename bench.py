@@ -229,6 +229,7 @@ def run_ours(args, cfg):
         check = {"rows_checked": rows, "violations": bad, "max_abs_err": max_abs, "max_rel_err": max_rel,
                  "rtol": 1e-5, "atol": 1e-6}
     del full
+    barrier()  # the next step overwrites the buffers rank 0 has just read
     graphed = (not args.no_graph) and op.capture(alpha, beta)
 
     # ---- device-resident steps
@@ -261,8 +262,9 @@ def run_ours(args, cfg):
     ms_total = max_over_ranks(float(sum(per_step)))
     ms_step = ms_total / args.steps
 
-    # ---- the product kernels alone (no gather), for the roofline
+    # ---- the product kernels alone (no reassembly: mirrors of the output cleared), for the roofline
     k_ms = None
+    op.reassemble_in_kernel(False)
     if hasattr(op, "op") and op.r1 > op.r0:
         ks = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
         ke = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
@@ -275,6 +277,7 @@ def run_ours(args, cfg):
         torch.cuda.synchronize()
         k_ms = float(np.mean([s.elapsed_time(e) for s, e in zip(ks, ke)]))
     k_ms = max_over_ranks(k_ms if k_ms is not None else 0.0)
+    op.reassemble_in_kernel(True)
 
     # ---- end to end from host buffers through the C API
     e2e = None
@@ -325,10 +328,10 @@ def run_ours(args, cfg):
         "clocks": clocks,
         # tile kernel + carry fix-up kernel (+ the push kernel at N > 1) per timed step and rank
         "gpu_launches": (3 if world > 1 and op.gather_mode == "push" else 2) * args.steps,
-        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                     "frac": achieved / peak if achieved else None, "traffic": None, "peak_kind": peak_kind,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak * world, "peak_per_gpu": peak, "unit": "GB/s",
+                     "frac": achieved / (peak * world) if achieved else None, "traffic": None, "peak_kind": peak_kind,
                      "algorithmic_bytes_per_launch": abytes, "kernel_ms": k_ms,
-                     "frac_of_nominal_8000": achieved / 8000.0 if achieved else None,
+                     "frac_of_nominal_8000": achieved / (8000.0 * world) if achieved else None,
                      "kernels": "SpmvTileKernel + SpmvCarryFixupKernel" if spmv else
                                 "SpmmTileKernel + SpmmCarryFixupKernel",
                      "hbm_gbs_at_step_time": abytes / (ms_step * 1e-3) / 1e9},
@@ -358,9 +361,10 @@ def main():
     ap.add_argument("--check-rows", type=int, default=1 << 20, help="rows compared with the oracle before timing")
     ap.add_argument("--cpu-rows", type=int, default=1 << 22, help="row block the CPU baseline runs on")
     ap.add_argument("--cpu-repeats", type=int, default=3)
-    ap.add_argument("--gather", default="fused", choices=["fused", "push", "nccl"],
-                    help="reassembly of y/C at N > 1: mirror stores inside the product kernels (default), "
-                    "a separate peer-store kernel, or the NCCL all-gather")
+    ap.add_argument("--gather", default="multicast", choices=["multicast", "fused", "push", "nccl"],
+                    help="reassembly of y/C at N > 1: multimem.st to the NVLink multicast address inside the "
+                    "product kernels (default), per-peer mirror stores inside them, a separate peer-store "
+                    "kernel, or the NCCL all-gather")
     ap.add_argument("--no-graph", action="store_true", help="launch every step kernel by kernel instead of "
                     "replaying the step as one CUDA graph")
     ap.add_argument("--no-check", action="store_true")

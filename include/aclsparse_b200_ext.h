@@ -50,6 +50,14 @@ aclsparseStatus_t aclsparseB200SpMVNoAlloc(aclrtStream stream, int64_t rows, int
 aclsparseStatus_t aclsparseB200DnVecSetMirrors(aclsparseDnVecDescr_t vec, int count, void* const* mirrors);
 aclsparseStatus_t aclsparseB200DnMatSetMirrors(aclsparseDnMatDescr_t mat, int count, void* const* mirrors);
 
+/* The same with ONE mirror that is an NVLink multicast address (a cuMulticast / symmetric-memory mapping
+ * bound to the result buffers of all GPUs of the node, advanced to this device's row block): the kernels
+ * store to it with multimem.st, NVSwitch replicates each store to every GPU, and a device sends its block
+ * once instead of once per peer.  Replaces any mirror list; SetMirrors(.., 0, NULL) clears it.  Only on
+ * devices and buffers for which such a mapping exists.  No counterpart in the reference. */
+aclsparseStatus_t aclsparseB200DnVecSetMulticastMirror(aclsparseDnVecDescr_t vec, void* multicast);
+aclsparseStatus_t aclsparseB200DnMatSetMulticastMirror(aclsparseDnMatDescr_t mat, void* multicast);
+
 #ifdef __cplusplus
 }
 #endif

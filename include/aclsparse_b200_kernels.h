@@ -23,8 +23,11 @@ extern "C" {
  * same element position of up to ACLSP_MAX_MIRRORS further buffers - the result buffers of the other GPUs
  * of the node, mapped into this device's address space - so that the product and the reassembly of the
  * sharded result over NVLink are one kernel.  mirrorDelta[m] is the BYTE distance from the output base to
- * mirror m's base.  Plain stores only; the caller's barrier follows the launch.  The reference library is
- * single-device and has nothing of the kind. */
+ * mirror m's base.  Plain stores only; the caller's barrier follows the launch.  With mirrorMulticast != 0
+ * there is exactly one mirror and it is an NVLink multicast address bound to the result buffers of all GPUs:
+ * the kernels write it with multimem.st and the switch delivers one copy to every GPU, so each device sends
+ * its row block once instead of once per peer.  The reference library is single-device and has nothing of
+ * the kind. */
 #define ACLSP_MAX_MIRRORS 7
 
 /* Per-launch parameters of the SpMV kernels.  Counterpart of the reference's
@@ -44,7 +47,7 @@ typedef struct AclspSpmvParams {
     const float* alphaPtr;   /* device pointer mode: scalars are read on the device */
     const float* betaPtr;
     uint32_t numMirrors;     /* 0: y only */
-    uint32_t reserved;
+    uint32_t mirrorMulticast;
     int64_t mirrorDelta[ACLSP_MAX_MIRRORS];
 } AclspSpmvParams;
 
@@ -68,7 +71,7 @@ typedef struct AclspSpmmParams {
     const float* alphaPtr;
     const float* betaPtr;
     uint32_t numMirrors;     /* 0: C only */
-    uint32_t reserved2;
+    uint32_t mirrorMulticast;
     int64_t mirrorDelta[ACLSP_MAX_MIRRORS];
 } AclspSpmmParams;
 

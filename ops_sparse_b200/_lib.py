@@ -58,7 +58,7 @@ class SpmvParams(ctypes.Structure):
     _fields_ = [("rows", c_uint32), ("cols", c_uint32), ("nnz", c_uint32), ("indexBase", c_uint32),
                 ("colIndStride", c_int64), ("valuesStride", c_int64), ("xStride", c_int64), ("yStride", c_int64),
                 ("alpha", c_float), ("beta", c_float), ("alphaPtr", c_void_p), ("betaPtr", c_void_p),
-                ("numMirrors", c_uint32), ("reserved", c_uint32), ("mirrorDelta", c_int64 * 7)]
+                ("numMirrors", c_uint32), ("mirrorMulticast", c_uint32), ("mirrorDelta", c_int64 * 7)]
 
 
 class SpmmParams(ctypes.Structure):
@@ -67,7 +67,7 @@ class SpmmParams(ctypes.Structure):
                 ("n", c_uint32), ("opB", c_uint32), ("orderB", c_uint32), ("orderC", c_uint32),
                 ("highPrecision", c_uint32), ("reserved", c_uint32), ("ldb", c_int64), ("ldc", c_int64), ("alpha", c_float), ("beta", c_float),
                 ("alphaPtr", c_void_p), ("betaPtr", c_void_p),
-                ("numMirrors", c_uint32), ("reserved2", c_uint32), ("mirrorDelta", c_int64 * 7)]
+                ("numMirrors", c_uint32), ("mirrorMulticast", c_uint32), ("mirrorDelta", c_int64 * 7)]
 
 
 _P = c_void_p
@@ -132,6 +132,8 @@ SIGNATURES = {
     "aclsparseB200SpMVNoAlloc": [_P, c_int64, c_int64, c_int64, _P, _P, _P, c_int, _P, _P, c_float, c_float],
     "aclsparseB200DnVecSetMirrors": [_P, c_int, POINTER(c_void_p)],
     "aclsparseB200DnMatSetMirrors": [_P, c_int, POINTER(c_void_p)],
+    "aclsparseB200DnVecSetMulticastMirror": [_P, _P],
+    "aclsparseB200DnMatSetMulticastMirror": [_P, _P],
     # include/aclsparse_b200_kernels.h
     "spmv_b200_preprocess_kernel_do": [_P, _P, c_uint32, c_uint32, c_uint32, c_int32, c_int64, _P],
     "spmv_b200_kernel_do": [_P, _P, _P, _P, _P, POINTER(SpmvParams), _P],

@@ -122,6 +122,11 @@ class DnVec:
         arr = (c_void_p * max(len(pointers), 1))(*[int(p) for p in pointers])
         check("aclsparseB200DnVecSetMirrors", L.lib().aclsparseB200DnVecSetMirrors(self._d, len(pointers), arr))
 
+    def set_multicast_mirror(self, pointer: int) -> None:
+        """NVLink multicast address that receives (on every GPU bound to it) each element SpMV writes."""
+        check("aclsparseB200DnVecSetMulticastMirror",
+              L.lib().aclsparseB200DnVecSetMulticastMirror(self._d, c_void_p(int(pointer))))
+
     def close(self) -> None:
         if self._d:
             L.lib().aclsparseDestroyDnVec(self._d)
@@ -153,6 +158,11 @@ class DnMat:
         """Device addresses (ints) of buffers that receive every element SpMM writes to this matrix."""
         arr = (c_void_p * max(len(pointers), 1))(*[int(p) for p in pointers])
         check("aclsparseB200DnMatSetMirrors", L.lib().aclsparseB200DnMatSetMirrors(self._d, len(pointers), arr))
+
+    def set_multicast_mirror(self, pointer: int) -> None:
+        """NVLink multicast address that receives (on every GPU bound to it) each element SpMM writes."""
+        check("aclsparseB200DnMatSetMulticastMirror",
+              L.lib().aclsparseB200DnMatSetMulticastMirror(self._d, c_void_p(int(pointer))))
 
     def close(self) -> None:
         if self._d:

@@ -52,13 +52,38 @@ aclsparseStatus_t SetMirrors(Descr* d, uint32_t signature, int count, void* cons
         }
     }
     d->numMirrors = count;
+    d->mirrorMulticast = false;
     for (int m = 0; m < ACLSP_MAX_MIRRORS; ++m) {
         d->mirrors[m] = m < count ? mirrors[m] : nullptr;
     }
     return ACL_SPARSE_STATUS_SUCCESS;
 }
 
+template <typename Descr>
+aclsparseStatus_t SetMulticastMirror(Descr* d, uint32_t signature, void* multicast)
+{
+    if (multicast == nullptr) {
+        return ACL_SPARSE_STATUS_INVALID_VALUE;
+    }
+    void* const one[1] = {multicast};
+    const aclsparseStatus_t st = SetMirrors(d, signature, 1, one);
+    if (st == ACL_SPARSE_STATUS_SUCCESS) {
+        d->mirrorMulticast = true;
+    }
+    return st;
+}
+
 }  // namespace
+
+extern "C" aclsparseStatus_t aclsparseB200DnVecSetMulticastMirror(aclsparseDnVecDescr_t vec, void* multicast)
+{
+    return SetMulticastMirror(vec, kDnVecSignature, multicast);
+}
+
+extern "C" aclsparseStatus_t aclsparseB200DnMatSetMulticastMirror(aclsparseDnMatDescr_t mat, void* multicast)
+{
+    return SetMulticastMirror(mat, kDnMatSignature, multicast);
+}
 
 extern "C" aclsparseStatus_t aclsparseB200DnVecSetMirrors(aclsparseDnVecDescr_t vec, int count, void* const* mirrors)
 {

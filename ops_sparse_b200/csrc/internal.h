@@ -120,6 +120,7 @@ struct aclsparseDnVecDescr {
     aclDataType valueType = ACL_FLOAT;
     // aclsparseB200DnVecSetMirrors: further buffers that receive every element SpMV writes.
     int numMirrors = 0;
+    bool mirrorMulticast = false;
     void* mirrors[7] = {};
 };
 
@@ -135,6 +136,7 @@ struct aclsparseDnMatDescr {
     int64_t batchStride = 0;
     // aclsparseB200DnMatSetMirrors: further buffers that receive every element SpMM writes.
     int numMirrors = 0;
+    bool mirrorMulticast = false;
     void* mirrors[7] = {};
 };
 

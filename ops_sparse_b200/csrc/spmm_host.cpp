@@ -294,6 +294,7 @@ extern "C" aclsparseStatus_t aclsparseSpMM(aclsparseHandle_t handle, aclsparseOp
         params.beta = *static_cast<const float*>(beta);
     }
     params.numMirrors = static_cast<uint32_t>(matC->numMirrors);
+    params.mirrorMulticast = matC->mirrorMulticast ? 1u : 0u;
     for (int m = 0; m < matC->numMirrors; ++m) {
         params.mirrorDelta[m] = static_cast<const char*>(matC->mirrors[m]) - static_cast<const char*>(matC->values);
         if (params.mirrorDelta[m] % 4 != 0) {

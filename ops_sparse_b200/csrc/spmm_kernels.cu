@@ -98,6 +98,22 @@ struct Vec<1> {
     using T = float;
 };
 
+// Store to an NVLink multicast address: the switch delivers it to every GPU.
+__device__ __forceinline__ void MulticastStore(void* addr, const float4& v)
+{
+    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};\n" ::"l"(addr), "f"(v.x), "f"(v.y),
+                 "f"(v.z), "f"(v.w)
+                 : "memory");
+}
+__device__ __forceinline__ void MulticastStore(void* addr, const float2& v)
+{
+    asm volatile("multimem.st.relaxed.sys.global.v2.f32 [%0], {%1, %2};\n" ::"l"(addr), "f"(v.x), "f"(v.y) : "memory");
+}
+__device__ __forceinline__ void MulticastStore(void* addr, const float& v)
+{
+    asm volatile("multimem.st.relaxed.sys.global.f32 [%0], %1;\n" ::"l"(addr), "f"(v) : "memory");
+}
+
 template <int BYTES>
 __device__ __forceinline__ void CpAsync(void* smem, const void* gmem)
 {
@@ -317,8 +333,12 @@ SpmmTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ val
             *reinterpret_cast<V*>(dst) = out;
             // Mirrors of C (the other GPUs' result buffers when the matrix is
             // sharded) receive the same 32 * VW contiguous floats per warp.
-            for (uint32_t m = 0; m < p.numMirrors; ++m) {
-                *reinterpret_cast<V*>(reinterpret_cast<char*>(dst) + p.mirrorDelta[m]) = out;
+            if (p.mirrorMulticast != 0) {
+                MulticastStore(reinterpret_cast<char*>(dst) + p.mirrorDelta[0], out);
+            } else {
+                for (uint32_t m = 0; m < p.numMirrors; ++m) {
+                    *reinterpret_cast<V*>(reinterpret_cast<char*>(dst) + p.mirrorDelta[m]) = out;
+                }
             }
         };
         // A finished row goes to C, unless it is the warp's first row and its
@@ -527,8 +547,12 @@ __global__ void SpmmCarryFixupKernel(float* __restrict__ C, SpmmPlanView plan, A
             const double r = static_cast<double>(sc.alpha) * sum;
             const float out = static_cast<float>(sc.betaZero ? r : r + static_cast<double>(sc.beta) * *dst);
             *dst = out;
-            for (uint32_t m = 0; m < p.numMirrors; ++m) {
-                *reinterpret_cast<float*>(reinterpret_cast<char*>(dst) + p.mirrorDelta[m]) = out;
+            if (p.mirrorMulticast != 0) {
+                MulticastStore(reinterpret_cast<char*>(dst) + p.mirrorDelta[0], out);
+            } else {
+                for (uint32_t m = 0; m < p.numMirrors; ++m) {
+                    *reinterpret_cast<float*>(reinterpret_cast<char*>(dst) + p.mirrorDelta[m]) = out;
+                }
             }
         }
     }

@@ -407,6 +407,7 @@ extern "C" aclsparseStatus_t aclsparseSpMV(aclsparseHandle_t handle, aclsparseOp
         params.beta = *static_cast<const float*>(beta);
     }
     params.numMirrors = static_cast<uint32_t>(vecY->numMirrors);
+    params.mirrorMulticast = vecY->mirrorMulticast ? 1u : 0u;
     for (int m = 0; m < vecY->numMirrors; ++m) {
         params.mirrorDelta[m] = static_cast<const char*>(vecY->mirrors[m]) - static_cast<const char*>(vecY->values);
         if (params.mirrorDelta[m] % 4 != 0) {

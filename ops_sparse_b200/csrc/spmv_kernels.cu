@@ -100,7 +100,8 @@ __device__ __forceinline__ Scalars LoadScalars(const AclspSpmvParams& p)
 
 // beta == 0 must not read y: it may hold NaN or be uninitialised.  The value
 // also goes to the same element of every mirror of y (the other GPUs' result
-// buffers when the matrix is sharded): plain stores, never read back.
+// buffers when the matrix is sharded): plain stores, or one multimem.st to a
+// multicast address; never read back.
 __device__ __forceinline__ void StoreRow(float* __restrict__ y, int64_t index, double sum, const Scalars& s,
                                          const AclspSpmvParams& p)
 {
@@ -108,6 +109,14 @@ __device__ __forceinline__ void StoreRow(float* __restrict__ y, int64_t index, d
     const float out = static_cast<float>(r);
     float* dst = y + index;
     *dst = out;
+    if (p.mirrorMulticast != 0) {
+        // One store to the multicast address; the switch copies it to every GPU.
+        asm volatile("multimem.st.relaxed.sys.global.f32 [%0], %1;\n" ::"l"(reinterpret_cast<char*>(dst) +
+                                                                                 p.mirrorDelta[0]),
+                     "f"(out)
+                     : "memory");
+        return;
+    }
     for (uint32_t m = 0; m < p.numMirrors; ++m) {
         *reinterpret_cast<float*>(reinterpret_cast<char*>(dst) + p.mirrorDelta[m]) = out;
     }

@@ -8,9 +8,14 @@ into ``world_size`` contiguous row blocks that balance the non-zeros:
 Rank g holds rows [bounds[g], bounds[g+1]) of A (row offsets rebased to start at
 0, its slice of the column indices and values), a full replica of x or B, and
 computes its slice of y or C with the single-GPU operators.  The only exchange
-is the reassembly of y / C on every rank, in one of three ways:
+is the reassembly of y / C on every rank, in one of four ways:
 
-* ``fused`` (default on GPUs): the result lives in a symmetric-memory buffer that
+* ``multicast`` (default on GPUs): as ``fused`` below, but the single mirror is the
+  NVLink multicast address of the symmetric buffer: the kernels write finished
+  rows with ``multimem.st`` and NVSwitch delivers them to every GPU, so a rank
+  sends its row block once, not once per peer.  Falls back to ``fused`` where the
+  buffer has no multicast mapping.
+* ``fused``: the result lives in a symmetric-memory buffer that
   every rank maps, and the peers' buffers are registered as mirrors of the local
   output (``aclsparseB200DnVecSetMirrors`` / ``DnMatSetMirrors``): the product
   kernels store each finished row into all ranks' buffers themselves, over
@@ -80,10 +85,10 @@ class _PushGather:
     it then must copy it first, exactly as with a reused all-gather output.
     """
 
-    def __init__(self, bounds: np.ndarray, rank: int, width: int, device, group=None, fused=False):
+    def __init__(self, bounds: np.ndarray, rank: int, width: int, device, group=None, fused=False, multicast=False):
         import torch.distributed._symmetric_memory as symm
-        # Only plain peer stores are used here; keep the buffer off NVLink multicast objects.
-        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        if not multicast:  # plain peer stores only: keep the buffer off NVLink multicast objects
+            os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         self.rank, self.width = rank, width
         self.world = bounds.size - 1
         group = group if group is not None else dist.group.WORLD
@@ -101,6 +106,8 @@ class _PushGather:
         self.fused = fused
         # Peers' addresses of this rank's row block: the mirrors of the local output in fused mode.
         self.mirror_ptrs = [p + self.offset * 4 for p in ptrs]
+        mc = int(getattr(self.handle, "multicast_ptr", 0) or 0) if multicast else 0
+        self.multicast_ptr = mc + self.offset * 4 if mc else 0
         self._lib = L.lib()
 
     def run(self) -> torch.Tensor:
@@ -115,9 +122,10 @@ class _PushGather:
 def _make_gather(mode: str, bounds, rank, width, device, group):
     """``fused`` / ``push`` where symmetric memory can be set up, else the all-gather; returns (gather, mode used)."""
     world = bounds.size - 1
-    if mode in ("fused", "push") and world > 1 and torch.device(device).type == "cuda":
+    if mode in ("multicast", "fused", "push") and world > 1 and torch.device(device).type == "cuda":
         try:
-            return _PushGather(bounds, rank, width, device, group, fused=mode == "fused"), mode
+            g = _PushGather(bounds, rank, width, device, group, fused=mode != "push", multicast=mode == "multicast")
+            return g, ("fused" if mode == "multicast" and not g.multicast_ptr else mode)
         except Exception as err:  # symmetric memory is optional plumbing; the all-gather gives the same result
             import warnings
             warnings.warn(f"symmetric-memory push unavailable ({err!r}); using the NCCL all-gather")
@@ -133,6 +141,18 @@ class _GraphedStep:
     """
 
     _graph = None
+    _out = None
+
+    def reassemble_in_kernel(self, on: bool) -> None:
+        """Registers (or clears) the other ranks' buffers as mirrors of the local output (fused / multicast)."""
+        if self._out is None or self.gather_mode not in ("fused", "multicast"):
+            return
+        if not on:
+            self._out.set_mirrors([])
+        elif self.gather_mode == "multicast":
+            self._out.set_multicast_mirror(self.gather.multicast_ptr)
+        else:
+            self._out.set_mirrors(self.gather.mirror_ptrs)
 
     def capture(self, alpha: float, beta: float) -> bool:
         """Records ``step(alpha, beta)`` into a graph that later ``step`` calls with the same scalars replay."""
@@ -169,7 +189,7 @@ class ShardedSpMV(_GraphedStep):
     partition / gather logic without a GPU; there is no CPU implementation in this package.)
     """
 
-    def __init__(self, cfg: dict, rank: int, world: int, device, group=None, local_product=None, gather="fused"):
+    def __init__(self, cfg: dict, rank: int, world: int, device, group=None, local_product=None, gather="multicast"):
         self.rank, self.world, self.device = rank, world, device
         base = cfg.get("index_base", 0)
         self.bounds = row_block_bounds_host(cfg["row_ptr"], cfg["nnz"], world, base)
@@ -191,8 +211,8 @@ class ShardedSpMV(_GraphedStep):
                                      nnz=int(self.local_col.size))
             self.op = api.SpMV(self.handle, self.mat, api.DnVec(self.x), api.DnVec(self.y_local,
                                                                                    size=self.r1 - self.r0))
-            if self.gather_mode == "fused":
-                self.op.y.set_mirrors(self.gather.mirror_ptrs)
+            self._out = self.op.y
+            self.reassemble_in_kernel(True)
             if self.r1 > self.r0:
                 self.op.preprocess()
 
@@ -207,7 +227,7 @@ class ShardedSpMV(_GraphedStep):
 class ShardedSpMM(_GraphedStep):
     """C = alpha * A * B + beta * C (row-major B and C) with A row-block sharded over the ranks."""
 
-    def __init__(self, cfg: dict, rank: int, world: int, device, group=None, local_product=None, gather="fused"):
+    def __init__(self, cfg: dict, rank: int, world: int, device, group=None, local_product=None, gather="multicast"):
         self.rank, self.world, self.device = rank, world, device
         base = cfg.get("index_base", 0)
         n = cfg["n"]
@@ -232,8 +252,8 @@ class ShardedSpMM(_GraphedStep):
             if rows > 0:
                 self.op = api.SpMM(self.handle, self.mat, api.DnMat(cfg["cols"], n, n, self.b),
                                    api.DnMat(rows, n, n, self.c_local))
-                if self.gather_mode == "fused":
-                    self.op.c.set_mirrors(self.gather.mirror_ptrs)
+                self._out = self.op.c
+                self.reassemble_in_kernel(True)
                 self.op.preprocess()
 
     def _eager_step(self, alpha: float, beta: float) -> torch.Tensor:
