@@ -37,6 +37,8 @@
  */
 #include <cstdint>
 
+#include <cstdlib>
+
 #include <cuda_runtime.h>
 
 #include "aclsparse_b200_kernels.h"
@@ -98,27 +100,43 @@ __device__ __forceinline__ Scalars LoadScalars(const AclspSpmvParams& p)
     return s;
 }
 
-// beta == 0 must not read y: it may hold NaN or be uninitialised.  The value
-// also goes to the same element of every mirror of y (the other GPUs' result
-// buffers when the matrix is sharded): plain stores, or one multimem.st to a
-// multicast address; never read back.
-__device__ __forceinline__ void StoreRow(float* __restrict__ y, int64_t index, double sum, const Scalars& s,
-                                         const AclspSpmvParams& p)
+// beta == 0 must not read y: it may hold NaN or be uninitialised.
+__device__ __forceinline__ float StoreRow(float* __restrict__ y, int64_t index, double sum, const Scalars& s)
 {
     const double r = s.betaZero ? s.alpha * sum : s.alpha * sum + s.beta * static_cast<double>(y[index]);
     const float out = static_cast<float>(r);
-    float* dst = y + index;
-    *dst = out;
-    if (p.mirrorMulticast != 0) {
-        // One store to the multicast address; the switch copies it to every GPU.
+    y[index] = out;
+    return out;
+}
+
+// Mirrors of y (the other GPUs' result buffers when the matrix is sharded)
+// receive what y received: plain stores to each mirror, or one multimem.st to
+// a multicast address that the switch copies to every GPU.  Never read back.
+__device__ __forceinline__ void MirrorStore(float* dst, float v, const AclspSpmvParams& p)
+{
+    if ((p.mirrorMulticast & 1u) != 0) {
         asm volatile("multimem.st.relaxed.sys.global.f32 [%0], %1;\n" ::"l"(reinterpret_cast<char*>(dst) +
                                                                                  p.mirrorDelta[0]),
-                     "f"(out)
+                     "f"(v)
                      : "memory");
         return;
     }
     for (uint32_t m = 0; m < p.numMirrors; ++m) {
-        *reinterpret_cast<float*>(reinterpret_cast<char*>(dst) + p.mirrorDelta[m]) = out;
+        *reinterpret_cast<float*>(reinterpret_cast<char*>(dst) + p.mirrorDelta[m]) = v;
+    }
+}
+
+__device__ __forceinline__ void MirrorStore(float4* dst, const float4& v, const AclspSpmvParams& p)
+{
+    if ((p.mirrorMulticast & 1u) != 0) {
+        asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};\n" ::"l"(
+                         reinterpret_cast<char*>(dst) + p.mirrorDelta[0]),
+                     "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w)
+                     : "memory");
+        return;
+    }
+    for (uint32_t m = 0; m < p.numMirrors; ++m) {
+        *reinterpret_cast<float4*>(reinterpret_cast<char*>(dst) + p.mirrorDelta[m]) = v;
     }
 }
 
@@ -185,6 +203,9 @@ SpmvTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ val
     float* sHi = sPool;
     float* sLo = sPool + span;
     int* sOff = reinterpret_cast<int*>(sPool + 2 * kTile + 24) - (nr + 2);
+    // nr more words fit between the products and the offsets (2 * span <= 2 * nt + 12 and
+    // nt + nr <= kTile): the finished rows' values, kept for the mirrors of y.
+    float* sOut = reinterpret_cast<float*>(sOff) - nr;
     if (tid == 0) {
         sNumLong = 0;
         sNumWarpSeg = 0;
@@ -264,6 +285,7 @@ SpmvTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ val
     const float* hiT = sHi + shift;     // product k of the tile
     const float* loT = sLo + shift;
 
+    const bool batchMirrors = (p.mirrorMulticast & 2u) != 0;
     auto segBegin = [&](int k) { const int b = sOff[k]; return b < 0 ? 0 : (b > nt ? nt : b); };
     auto segEnd = [&](int k) {
         if (k >= nr) {
@@ -278,7 +300,15 @@ SpmvTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ val
         } else if (k == 0 && headOpen) {
             plan.carry[2 * t + 1] = sum;
         } else {
-            StoreRow(y, static_cast<int64_t>(i0 + k) * p.yStride, sum, sc, p);
+            float* at = y + static_cast<int64_t>(i0 + k) * p.yStride;
+            const float out = StoreRow(at, 0, sum, sc);
+            if (p.numMirrors != 0) {
+                if (batchMirrors) {
+                    sOut[k] = out;
+                } else {
+                    MirrorStore(at, out, p);
+                }
+            }
         }
     };
     // Sum of products [b, e) taken by this thread with the given stride: the hi
@@ -382,6 +412,43 @@ SpmvTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ val
         }
         __syncthreads();
     }
+
+    // Mirrors, batched: the rows this tile finished are one contiguous run of
+    // y.  Their values were kept in shared memory and now go out as whole
+    // 16-byte vectors wherever y and the mirrors allow, so that the links carry
+    // full lines instead of one packet per row.
+    if (p.numMirrors != 0 && batchMirrors) {
+        __syncthreads();
+        const int skip = headOpen ? 1 : 0;
+        const int count = nr - skip;
+        const float* vals = sOut + skip;
+        if (p.yStride == 1) {
+            float* run = y + i0 + skip;
+            bool aligned = true;  // a mirror is as aligned as y and its distance from y
+            for (uint32_t m = 0; m < p.numMirrors; ++m) {
+                aligned = aligned && (p.mirrorDelta[m] & 15) == 0;
+            }
+            int head = static_cast<int>((16u - (reinterpret_cast<uintptr_t>(run) & 15u)) & 15u) >> 2;
+            head = aligned ? (head < count ? head : count) : count;
+            head = head < 0 ? 0 : head;
+            const int vecs = (count - head) >> 2;
+            for (int k = tid; k < head; k += kThreads) {
+                MirrorStore(run + k, vals[k], p);
+            }
+            for (int v = tid; v < vecs; v += kThreads) {
+                const int k = head + 4 * v;
+                MirrorStore(reinterpret_cast<float4*>(run + k), make_float4(vals[k], vals[k + 1], vals[k + 2], vals[k + 3]),
+                            p);
+            }
+            for (int k = head + 4 * (vecs > 0 ? vecs : 0) + tid; k < count; k += kThreads) {
+                MirrorStore(run + k, vals[k], p);
+            }
+        } else {
+            for (int k = tid; k < count; k += kThreads) {
+                MirrorStore(y + static_cast<int64_t>(i0 + skip + k) * p.yStride, vals[k], p);
+            }
+        }
+    }
 }
 
 // One thread per tile whose first row began in an earlier tile and ends in
@@ -415,7 +482,11 @@ __global__ void SpmvCarryFixupKernel(float* __restrict__ y, SpmvPlanView plan, A
         sum += plan.carry[2 * u];
     }
     sum += plan.carry[2 * t + 1];
-    StoreRow(y, static_cast<int64_t>(i0) * p.yStride, sum, LoadScalars(p), p);
+    float* at = y + static_cast<int64_t>(i0) * p.yStride;
+    const float out = StoreRow(at, 0, sum, LoadScalars(p));
+    if (p.numMirrors != 0) {
+        MirrorStore(at, out, p);
+    }
 }
 
 }  // namespace
@@ -424,7 +495,19 @@ extern "C" void spmv_b200_kernel_do(const void* colInd, const void* values, cons
                                     void* workspace, const AclspSpmvParams* params, void* stream)
 {
     auto s = static_cast<cudaStream_t>(stream);
-    const AclspSpmvParams p = *params;
+    AclspSpmvParams p = *params;
+    // Bit 1 of mirrorMulticast (internal): send a tile's finished rows to the mirrors as one contiguous
+    // run of 16-byte vectors after the tile, instead of row by row as they are produced.  Row by row costs
+    // the kernel nothing but arrives as 32- to 64-byte packets (about 185 GB/s into a B200, measured), enough
+    // for one or two peers; batching costs a barrier per tile (+10 % kernel time) and is what keeps 8 GPUs
+    // fed.  ACLSPARSE_SPMV_MIRROR_BATCH=0 / 1 overrides the choice.
+    static const int batchEnv = [] {
+        const char* e = std::getenv("ACLSPARSE_SPMV_MIRROR_BATCH");
+        return e == nullptr ? -1 : (e[0] == '1' ? 1 : 0);
+    }();
+    const bool multicast = (p.mirrorMulticast & 1u) != 0;
+    const bool batch = batchEnv >= 0 ? batchEnv == 1 : (multicast || p.numMirrors >= 3);
+    p.mirrorMulticast = (multicast ? 1u : 0u) | (batch ? 2u : 0u);
     const SpmvPlanView plan = MakeView(workspace, p.rows, p.nnz);
     if (plan.numTiles == 0) {
         return;

@@ -13,8 +13,8 @@ is the reassembly of y / C on every rank, in one of four ways:
 * ``multicast`` (default on GPUs): as ``fused`` below, but the single mirror is the
   NVLink multicast address of the symmetric buffer: the kernels write finished
   rows with ``multimem.st`` and NVSwitch delivers them to every GPU, so a rank
-  sends its row block once, not once per peer.  Falls back to ``fused`` where the
-  buffer has no multicast mapping.
+  sends its row block once, not once per peer.  ``fused`` is used instead at two
+  ranks and where the buffer has no multicast mapping.
 * ``fused``: the result lives in a symmetric-memory buffer that
   every rank maps, and the peers' buffers are registered as mirrors of the local
   output (``aclsparseB200DnVecSetMirrors`` / ``DnMatSetMirrors``): the product
@@ -122,6 +122,8 @@ class _PushGather:
 def _make_gather(mode: str, bounds, rank, width, device, group):
     """``fused`` / ``push`` where symmetric memory can be set up, else the all-gather; returns (gather, mode used)."""
     world = bounds.size - 1
+    if mode == "multicast" and world == 2:
+        mode = "fused"  # one peer: a multicast store saves nothing over the plain peer store
     if mode in ("multicast", "fused", "push") and world > 1 and torch.device(device).type == "cuda":
         try:
             g = _PushGather(bounds, rank, width, device, group, fused=mode != "push", multicast=mode == "multicast")
