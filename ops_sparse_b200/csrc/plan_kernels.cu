@@ -80,6 +80,7 @@ __global__ void TileSplitKernel(void* workspace, uint32_t rows, uint32_t cols, u
         h.carryOff = layout.carryOff;
         h.totalBytes = layout.totalBytes;
         *reinterpret_cast<AclspPlanHeader*>(base) = h;
+        *reinterpret_cast<uint32_t*>(base + ACLSP_HEADER_WAIT_FAILURES_OFF) = 0u;
     }
     if (t >= layout.numTiles) {
         return;

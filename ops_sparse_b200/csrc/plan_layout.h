@@ -37,6 +37,9 @@
 #define ACLSP_PLAN_VERSION 1u
 #define ACLSP_KIND_SPMV 1u
 #define ACLSP_KIND_SPMM 2u
+/* Byte offset, inside the header, of a uint32 that counts the CTAs of the persistent SpMV kernel whose
+ * bounded wait for a bulk copy ran out (0 after every healthy product; zeroed by the preprocessing pass). */
+#define ACLSP_HEADER_WAIT_FAILURES_OFF 128u
 
 /* Merge items per tile. */
 #define ACLSP_SPMV_TILE_ITEMS 2048u

@@ -157,133 +157,58 @@ __device__ __forceinline__ void Product(float a, int32_t rawCol, const float* __
     lo = fmaf(a, xv, -hi);
 }
 
-template <bool kVector>
-__global__ void __launch_bounds__(kThreads)
-SpmvTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ values, const float* __restrict__ x,
-               float* __restrict__ y, SpmvPlanView plan, AclspSpmvParams p)
+/* ------------------------------------------------------------- reduce -- */
+
+// Shared scratch of the reduction, one per CTA.
+struct ReduceScratch {
+    double warp[kWarps];
+    int longSeg[kMaxLong];
+    int warpSeg[kMaxWarpSeg];
+    int numLong;
+    int numWarpSeg;
+};
+
+// The staged tile: nt exact products (hi, lo), the nr + 1 row offsets relative
+// to the tile's first product, and nr spare words for the mirrors of y.
+struct StagedTile {
+    int t;
+    int i0;
+    int i1;
+    int nr;
+    int nt;
+    int cls;
+    const float* hiT;
+    const float* loT;
+    const int* sOff;
+    float* sOut;
+};
+
+// Reduces the rows of a staged tile and writes them (y, mirrors, carries).
+// Called by all threads of the CTA after the barrier that follows staging and
+// after thread 0 has zeroed scratch.numLong / numWarpSeg before that barrier.
+__device__ __forceinline__ void ReduceTile(const StagedTile& st, float* __restrict__ y, const SpmvPlanView& plan,
+                                           const AclspSpmvParams& p, ReduceScratch& scratch)
 {
-    // One pool of 32-bit words: the hi parts of the tile's products, their lo
-    // parts, and the tile's row offsets packed against the end.  A tile has nt
-    // products and nr + 1 offsets with nt + nr <= kTile.
-    __shared__ __align__(16) float sPool[2 * kTile + 24];
-    __shared__ double sWarp[kWarps];
-    __shared__ int sLong[kMaxLong];
-    __shared__ int sWarpSeg[kMaxWarpSeg];
-    __shared__ int sNumLong;
-    __shared__ int sNumWarpSeg;
-
     const int tid = threadIdx.x;
-    const int t = blockIdx.x;
-    const int nnz = static_cast<int>(p.nnz);
-    const int64_t total = static_cast<int64_t>(p.rows) + nnz;
-    int64_t d0 = static_cast<int64_t>(t) * kTile;
-    int64_t d1 = d0 + kTile;
-    d0 = d0 < total ? d0 : total;
-    d1 = d1 < total ? d1 : total;
-    const int i0 = plan.tileRow[t];
-    const int i1 = plan.tileRow[t + 1];
-    const int j0 = static_cast<int>(d0 - i0);
-    const int j1 = static_cast<int>(d1 - i1);
-    const int nr = i1 - i0;
-    const int nt = j1 - j0;
-    // Row offsets that are not non-decreasing can produce an inconsistent
-    // split; such a tile is skipped rather than trusted.
-    if (nr < 0 || nt < 0 || nr + nt > kTile || i0 < 0 || i1 > static_cast<int>(p.rows) || j0 < 0 || j1 > nnz) {
-        if (tid == 0) {
-            plan.carry[2 * t] = 0.0;
-            plan.carry[2 * t + 1] = 0.0;
-        }
-        return;
-    }
-    // Products are stored at their offset from the 4-aligned array index a0,
-    // so that a 128-bit load of the arrays maps onto a 128-bit shared store.
-    const int a0 = kVector ? (j0 & ~3) : j0;
-    const int shift = j0 - a0;
-    const int span = (nt + shift + 3) & ~3;
-    float* sHi = sPool;
-    float* sLo = sPool + span;
-    int* sOff = reinterpret_cast<int*>(sPool + 2 * kTile + 24) - (nr + 2);
-    // nr more words fit between the products and the offsets (2 * span <= 2 * nt + 12 and
-    // nt + nr <= kTile): the finished rows' values, kept for the mirrors of y.
-    float* sOut = reinterpret_cast<float*>(sOff) - nr;
-    if (tid == 0) {
-        sNumLong = 0;
-        sNumWarpSeg = 0;
-    }
-    for (int k = tid; k <= nr; k += kThreads) {
-        sOff[k] = ClampOffset(plan.rowPtr[i0 + k], nnz) - j0;
-    }
-
-    if (kVector) {
-        const int nvec = span >> 2;
-        struct Vec4 {
-            int4 c;
-            float4 w;
-        };
-        auto loadVec = [&](int v, Vec4& o) {
-            const int e = a0 + 4 * v;
-            if (e + 4 <= nnz) {
-                o.c = __ldcs(reinterpret_cast<const int4*>(colInd + e));
-                o.w = __ldcs(reinterpret_cast<const float4*>(values + e));
-            } else {  // the last vector of the arrays may be partial
-                int32_t c[4];
-                float w[4];
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    const bool in = e + q < nnz;
-                    c[q] = in ? __ldcs(colInd + e + q) : -1;
-                    w[q] = in ? __ldcs(values + e + q) : 0.0f;
-                }
-                o.c = make_int4(c[0], c[1], c[2], c[3]);
-                o.w = make_float4(w[0], w[1], w[2], w[3]);
-            }
-        };
-        // Elements of the first and last vector that belong to a neighbouring
-        // tile are multiplied too; nothing reads their slots.
-        auto useVec = [&](int v, const Vec4& o) {
-            float4 hi, lo;
-            Product(o.w.x, o.c.x, x, p.indexBase, p.cols, 1, hi.x, lo.x);
-            Product(o.w.y, o.c.y, x, p.indexBase, p.cols, 1, hi.y, lo.y);
-            Product(o.w.z, o.c.z, x, p.indexBase, p.cols, 1, hi.z, lo.z);
-            Product(o.w.w, o.c.w, x, p.indexBase, p.cols, 1, hi.w, lo.w);
-            *reinterpret_cast<float4*>(sHi + 4 * v) = hi;
-            *reinterpret_cast<float4*>(sLo + 4 * v) = lo;
-        };
-        // A tile spans at most kTile / 4 + 1 vectors: kVecsPerThread per thread,
-        // all of them loaded before the first is used, plus a one-vector remainder.
-        constexpr int kVecsPerThread = kTile / 4 / kThreads;
-        Vec4 vv[kVecsPerThread];
-#pragma unroll
-        for (int u = 0; u < kVecsPerThread; ++u) {
-            if (tid + u * kThreads < nvec) {
-                loadVec(tid + u * kThreads, vv[u]);
-            }
-        }
-#pragma unroll
-        for (int u = 0; u < kVecsPerThread; ++u) {
-            if (tid + u * kThreads < nvec) {
-                useVec(tid + u * kThreads, vv[u]);
-            }
-        }
-        for (int v = tid + kVecsPerThread * kThreads; v < nvec; v += kThreads) {
-            Vec4 vc;
-            loadVec(v, vc);
-            useVec(v, vc);
-        }
-    } else {
-        for (int k = tid; k < nt; k += kThreads) {
-            const int64_t e = static_cast<int64_t>(j0) + k;
-            Product(values[e * p.valuesStride], colInd[e * p.colIndStride], x, p.indexBase, p.cols, p.xStride,
-                    sHi[k], sLo[k]);
-        }
-    }
-    __syncthreads();
+    const int t = st.t;
+    const int i0 = st.i0;
+    const int i1 = st.i1;
+    const int nr = st.nr;
+    const int nt = st.nt;
+    const float* hiT = st.hiT;
+    const float* loT = st.loT;
+    const int* sOff = st.sOff;
+    float* sOut = st.sOut;
+    double* sWarp = scratch.warp;
+    int* sLong = scratch.longSeg;
+    int* sWarpSeg = scratch.warpSeg;
+    int& sNumLong = scratch.numLong;
+    int& sNumWarpSeg = scratch.numWarpSeg;
+    (void)i1;
 
     const Scalars sc = LoadScalars(p);
     const bool headOpen = sOff[0] < 0;  // row i0 began in an earlier tile
     const int nseg = nr + 1;            // rows ending here, then the open tail
-    const float* hiT = sHi + shift;     // product k of the tile
-    const float* loT = sLo + shift;
 
     const bool batchMirrors = (p.mirrorMulticast & 2u) != 0;
     auto segBegin = [&](int k) { const int b = sOff[k]; return b < 0 ? 0 : (b > nt ? nt : b); };
@@ -331,7 +256,7 @@ SpmvTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ val
     };
 
     // Vector per row: 2^cls lanes share a row piece.
-    const int cls = plan.tileClass[t] & 7;
+    const int cls = st.cls & 7;
     const int shiftLanes = cls > 5 ? 5 : cls;
     const int lanes = 1 << shiftLanes;
     const int lane = tid & (lanes - 1);
@@ -451,6 +376,408 @@ SpmvTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ val
     }
 }
 
+/* --------------------------------------------- one CTA per tile -- */
+
+template <bool kVector>
+__global__ void __launch_bounds__(kThreads)
+SpmvTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ values, const float* __restrict__ x,
+               float* __restrict__ y, SpmvPlanView plan, AclspSpmvParams p)
+{
+    // One pool of 32-bit words: the hi parts of the tile's products, their lo
+    // parts, and the tile's row offsets packed against the end.  A tile has nt
+    // products and nr + 1 offsets with nt + nr <= kTile.
+    __shared__ __align__(16) float sPool[2 * kTile + 24];
+    __shared__ ReduceScratch scratch;
+
+    const int tid = threadIdx.x;
+    const int t = blockIdx.x;
+    const int nnz = static_cast<int>(p.nnz);
+    const int64_t total = static_cast<int64_t>(p.rows) + nnz;
+    int64_t d0 = static_cast<int64_t>(t) * kTile;
+    int64_t d1 = d0 + kTile;
+    d0 = d0 < total ? d0 : total;
+    d1 = d1 < total ? d1 : total;
+    const int i0 = plan.tileRow[t];
+    const int i1 = plan.tileRow[t + 1];
+    const int j0 = static_cast<int>(d0 - i0);
+    const int j1 = static_cast<int>(d1 - i1);
+    const int nr = i1 - i0;
+    const int nt = j1 - j0;
+    // Row offsets that are not non-decreasing can produce an inconsistent
+    // split; such a tile is skipped rather than trusted.
+    if (nr < 0 || nt < 0 || nr + nt > kTile || i0 < 0 || i1 > static_cast<int>(p.rows) || j0 < 0 || j1 > nnz) {
+        if (tid == 0) {
+            plan.carry[2 * t] = 0.0;
+            plan.carry[2 * t + 1] = 0.0;
+        }
+        return;
+    }
+    // Products are stored at their offset from the 4-aligned array index a0,
+    // so that a 128-bit load of the arrays maps onto a 128-bit shared store.
+    const int a0 = kVector ? (j0 & ~3) : j0;
+    const int shift = j0 - a0;
+    const int span = (nt + shift + 3) & ~3;
+    float* sHi = sPool;
+    float* sLo = sPool + span;
+    int* sOff = reinterpret_cast<int*>(sPool + 2 * kTile + 24) - (nr + 2);
+    // nr more words fit between the products and the offsets (2 * span <= 2 * nt + 12 and
+    // nt + nr <= kTile): the finished rows' values, kept for the mirrors of y.
+    float* sOut = reinterpret_cast<float*>(sOff) - nr;
+    if (tid == 0) {
+        scratch.numLong = 0;
+        scratch.numWarpSeg = 0;
+    }
+    for (int k = tid; k <= nr; k += kThreads) {
+        sOff[k] = ClampOffset(plan.rowPtr[i0 + k], nnz) - j0;
+    }
+
+    if (kVector) {
+        const int nvec = span >> 2;
+        struct Vec4 {
+            int4 c;
+            float4 w;
+        };
+        auto loadVec = [&](int v, Vec4& o) {
+            const int e = a0 + 4 * v;
+            if (e + 4 <= nnz) {
+                o.c = __ldcs(reinterpret_cast<const int4*>(colInd + e));
+                o.w = __ldcs(reinterpret_cast<const float4*>(values + e));
+            } else {  // the last vector of the arrays may be partial
+                int32_t c[4];
+                float w[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const bool in = e + q < nnz;
+                    c[q] = in ? __ldcs(colInd + e + q) : -1;
+                    w[q] = in ? __ldcs(values + e + q) : 0.0f;
+                }
+                o.c = make_int4(c[0], c[1], c[2], c[3]);
+                o.w = make_float4(w[0], w[1], w[2], w[3]);
+            }
+        };
+        // Elements of the first and last vector that belong to a neighbouring
+        // tile are multiplied too; nothing reads their slots.
+        auto useVec = [&](int v, const Vec4& o) {
+            float4 hi, lo;
+            Product(o.w.x, o.c.x, x, p.indexBase, p.cols, 1, hi.x, lo.x);
+            Product(o.w.y, o.c.y, x, p.indexBase, p.cols, 1, hi.y, lo.y);
+            Product(o.w.z, o.c.z, x, p.indexBase, p.cols, 1, hi.z, lo.z);
+            Product(o.w.w, o.c.w, x, p.indexBase, p.cols, 1, hi.w, lo.w);
+            *reinterpret_cast<float4*>(sHi + 4 * v) = hi;
+            *reinterpret_cast<float4*>(sLo + 4 * v) = lo;
+        };
+        // A tile spans at most kTile / 4 + 1 vectors: kVecsPerThread per thread,
+        // all of them loaded before the first is used, plus a one-vector remainder.
+        constexpr int kVecsPerThread = kTile / 4 / kThreads;
+        Vec4 vv[kVecsPerThread];
+#pragma unroll
+        for (int u = 0; u < kVecsPerThread; ++u) {
+            if (tid + u * kThreads < nvec) {
+                loadVec(tid + u * kThreads, vv[u]);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < kVecsPerThread; ++u) {
+            if (tid + u * kThreads < nvec) {
+                useVec(tid + u * kThreads, vv[u]);
+            }
+        }
+        for (int v = tid + kVecsPerThread * kThreads; v < nvec; v += kThreads) {
+            Vec4 vc;
+            loadVec(v, vc);
+            useVec(v, vc);
+        }
+    } else {
+        for (int k = tid; k < nt; k += kThreads) {
+            const int64_t e = static_cast<int64_t>(j0) + k;
+            Product(values[e * p.valuesStride], colInd[e * p.colIndStride], x, p.indexBase, p.cols, p.xStride,
+                    sHi[k], sLo[k]);
+        }
+    }
+    __syncthreads();
+
+    StagedTile st;
+    st.t = t;
+    st.i0 = i0;
+    st.i1 = i1;
+    st.nr = nr;
+    st.nt = nt;
+    st.cls = plan.tileClass[t];
+    st.hiT = sHi + shift;  // product k of the tile
+    st.loT = sLo + shift;
+    st.sOff = sOff;
+    st.sOut = sOut;
+    ReduceTile(st, y, plan, p, scratch);
+}
+
+/* ------------------------------------- persistent, bulk-copy fed -- */
+
+// The same tile work inside a persistent CTA that never issues a global load
+// for the matrix: thread 0 asks the copy engine (cp.async.bulk, completion on an
+// mbarrier) for the tile's slice of values, colInd and row offsets kStreamStages
+// tiles ahead, straight into the shared-memory words where the products will
+// replace them.  Measured on B200 (27-point stencil, 4.1 M rows): the copies
+// alone stream at 6.7 TB/s, but a CTA needs about 3.6 us of dependent latency per
+// tile (x gather, barriers, reduction) whatever runs beside it, and the stages
+// leave room for only 4 CTAs per SM, so the whole product takes 0.33 ms against
+// 0.26 ms for the one-CTA-per-tile kernel with its 6 CTAs per SM.  It is
+// therefore opt-in (ACLSPARSE_SPMV_STREAM=1) and kept bit-identical to the
+// default kernel by the tests.
+constexpr int kStreamStages = 3;
+constexpr int kStageWords = 2 * kTile + 24;
+constexpr int kStreamCtasPerSm = 4;
+constexpr uint32_t kSpinLimit = 1u << 18;  // polls of about a microsecond before a wait is given up
+
+struct TileGeom {
+    int i0, i1, j0, nr, nt;
+    int a0, shift, span;     // first 4-aligned array index, distance of the tile's first product from it, words staged
+    int copyElems;           // leading part of the span that is whole vectors inside the arrays: bulk-copied
+    int offFirst, offShift;  // first 4-aligned row offset copied, distance of row i0 from it
+    int offWords;
+    bool valid;
+};
+
+__device__ __forceinline__ TileGeom Geometry(uint32_t t, int i0, int i1, const AclspSpmvParams& p)
+{
+    TileGeom g;
+    const int nnz = static_cast<int>(p.nnz);
+    const int64_t total = static_cast<int64_t>(p.rows) + nnz;
+    int64_t d0 = static_cast<int64_t>(t) * kTile;
+    int64_t d1 = d0 + kTile;
+    d0 = d0 < total ? d0 : total;
+    d1 = d1 < total ? d1 : total;
+    g.i0 = i0;
+    g.i1 = i1;
+    g.j0 = static_cast<int>(d0 - i0);
+    const int j1 = static_cast<int>(d1 - i1);
+    g.nr = i1 - i0;
+    g.nt = j1 - g.j0;
+    g.valid = !(g.nr < 0 || g.nt < 0 || g.nr + g.nt > kTile || i0 < 0 || i1 > static_cast<int>(p.rows) || g.j0 < 0 ||
+                j1 > nnz);
+    g.a0 = g.j0 & ~3;
+    g.shift = g.j0 - g.a0;
+    g.span = (g.nt + g.shift + 3) & ~3;
+    const int whole = (nnz & ~3) - g.a0;
+    g.copyElems = whole < 0 ? 0 : (whole < g.span ? whole : g.span);
+    g.offFirst = i0 & ~3;
+    g.offShift = i0 - g.offFirst;
+    g.offWords = (g.nr + 1 + g.offShift + 3) & ~3;
+    return g;
+}
+
+__device__ __forceinline__ uint32_t SharedAddress(const void* ptr)
+{
+    return static_cast<uint32_t>(__cvta_generic_to_shared(ptr));
+}
+
+__device__ __forceinline__ void BulkLoad(void* smemDst, const void* gmemSrc, uint32_t bytes, uint64_t* bar)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(
+                     SharedAddress(smemDst)),
+                 "l"(gmemSrc), "r"(bytes), "r"(SharedAddress(bar))
+                 : "memory");
+}
+
+// Thread 0: announce the bytes of a tile to the stage's barrier and start its copies.
+__device__ __forceinline__ void IssueTile(const TileGeom& g, float* stage, uint64_t* bar, const int32_t* colInd,
+                                          const float* values, const int32_t* rowPtr)
+{
+    const uint32_t arrayBytes = g.valid ? 4u * static_cast<uint32_t>(g.copyElems) : 0u;
+    const uint32_t offBytes = g.valid ? 4u * static_cast<uint32_t>(g.offWords) : 0u;
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(SharedAddress(bar)),
+                 "r"(2u * arrayBytes + offBytes)
+                 : "memory");
+    if (arrayBytes != 0) {
+        BulkLoad(stage, values + g.a0, arrayBytes, bar);
+        BulkLoad(stage + g.span, colInd + g.a0, arrayBytes, bar);
+    }
+    if (offBytes != 0) {
+        BulkLoad(stage + 2 * g.span, rowPtr + g.offFirst, offBytes, bar);
+    }
+}
+
+// Bounded wait for a stage: false when the copies have not landed after kSpinLimit polls.
+__device__ __forceinline__ bool WaitStage(uint64_t* bar, uint32_t parity)
+{
+    const uint32_t addr = SharedAddress(bar);
+    for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+        uint32_t done;
+        asm volatile(
+            "{\n"
+            ".reg .pred p;\n"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, 1000;\n"
+            "selp.u32 %0, 1, 0, p;\n"
+            "}\n"
+            : "=r"(done)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (done != 0) {
+            return true;
+        }
+    }
+    return false;
+}
+
+__global__ void __launch_bounds__(kThreads, kStreamCtasPerSm)
+SpmvStreamKernel(const int32_t* __restrict__ colInd, const float* __restrict__ values, const float* __restrict__ x,
+                 float* __restrict__ y, SpmvPlanView plan, AclspSpmvParams p, uint32_t* __restrict__ waitFailures)
+{
+    extern __shared__ __align__(128) unsigned char smemRaw[];
+    float* stages = reinterpret_cast<float*>(smemRaw);                                   // kStreamStages * kStageWords
+    uint64_t* full = reinterpret_cast<uint64_t*>(stages + kStreamStages * kStageWords);  // kStreamStages barriers
+    ReduceScratch& scratch = *reinterpret_cast<ReduceScratch*>(full + kStreamStages);
+
+    const int tid = threadIdx.x;
+    const int nnz = static_cast<int>(p.nnz);
+    const uint32_t numTiles = plan.numTiles;
+    const uint32_t stride = gridDim.x;
+
+    if (tid == 0) {
+        for (int sIdx = 0; sIdx < kStreamStages; ++sIdx) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(SharedAddress(full + sIdx)) : "memory");
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+        uint32_t t = blockIdx.x;
+        for (int sIdx = 0; sIdx < kStreamStages && t < numTiles; ++sIdx, t += stride) {
+            const TileGeom g = Geometry(t, plan.tileRow[t], plan.tileRow[t + 1], p);
+            IssueTile(g, stages + sIdx * kStageWords, full + sIdx, colInd, values, plan.rowPtr);
+        }
+    }
+    __syncthreads();
+
+    // Split points and row bin of the tile after this one, fetched a tile ahead.
+    uint32_t t = blockIdx.x;
+    int nextI0 = 0, nextI1 = 0, nextCls = 0;
+    if (t < numTiles) {
+        nextI0 = plan.tileRow[t];
+        nextI1 = plan.tileRow[t + 1];
+        nextCls = plan.tileClass[t];
+    }
+    bool waitedOut = false;
+    for (uint32_t it = 0; t < numTiles; ++it, t += stride) {
+        const int sIdx = static_cast<int>(it % kStreamStages);
+        const uint32_t parity = (it / kStreamStages) & 1u;
+        float* stage = stages + sIdx * kStageWords;
+        const TileGeom g = Geometry(t, nextI0, nextI1, p);
+        const int cls = nextCls;
+        const uint32_t tNext = t + stride;
+        if (tNext < numTiles) {
+            nextI0 = plan.tileRow[tNext];
+            nextI1 = plan.tileRow[tNext + 1];
+            nextCls = plan.tileClass[tNext];
+        }
+        // Thread 0 refills this stage after the tile: its split points are fetched now.
+        const uint32_t tRefill = t + kStreamStages * stride;
+        int refillI0 = 0, refillI1 = 0;
+        if (tid == 0 && tRefill < numTiles) {
+            refillI0 = plan.tileRow[tRefill];
+            refillI1 = plan.tileRow[tRefill + 1];
+        }
+        if (tid == 0) {
+            scratch.numLong = 0;
+            scratch.numWarpSeg = 0;
+        }
+        // A wait that runs out is recorded and the tile goes on with whatever the
+        // stage holds: indices are range-checked, so the worst outcome is a wrong
+        // value, and every thread keeps reaching the barriers below.
+        if (!waitedOut && !WaitStage(full + sIdx, parity)) {
+            waitedOut = true;  // and no further wait of this CTA is attempted
+        }
+
+        if (!g.valid) {
+            if (tid == 0) {
+                plan.carry[2 * t] = 0.0;
+                plan.carry[2 * t + 1] = 0.0;
+            }
+        } else {
+            float* sHi = stage;            // values, then the hi parts
+            float* sLo = stage + g.span;   // colInd, then the lo parts
+            int* sOff = reinterpret_cast<int*>(stage + 2 * g.span) + g.offShift;
+            float* sOut = stage + 2 * g.span + g.offWords;
+            for (int k = tid; k <= g.nr; k += kThreads) {
+                sOff[k] = ClampOffset(sOff[k], nnz) - g.j0;
+            }
+            const int nvec = g.span >> 2;
+            const int copied = g.copyElems >> 2;
+            struct Vec4 {
+                int4 c;
+                float4 w;
+            };
+            auto loadVec = [&](int v, Vec4& o) {
+                if (v < copied) {
+                    o.w = *reinterpret_cast<const float4*>(sHi + 4 * v);
+                    o.c = *reinterpret_cast<const int4*>(sLo + 4 * v);
+                } else {  // the last, partial vector of the arrays: plain loads
+                    const int e = g.a0 + 4 * v;
+                    int32_t c[4];
+                    float w[4];
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const bool in = e + q < nnz;
+                        c[q] = in ? __ldcs(colInd + e + q) : -1;
+                        w[q] = in ? __ldcs(values + e + q) : 0.0f;
+                    }
+                    o.c = make_int4(c[0], c[1], c[2], c[3]);
+                    o.w = make_float4(w[0], w[1], w[2], w[3]);
+                }
+            };
+            auto useVec = [&](int v, const Vec4& o) {
+                float4 hi, lo;
+                Product(o.w.x, o.c.x, x, p.indexBase, p.cols, 1, hi.x, lo.x);
+                Product(o.w.y, o.c.y, x, p.indexBase, p.cols, 1, hi.y, lo.y);
+                Product(o.w.z, o.c.z, x, p.indexBase, p.cols, 1, hi.z, lo.z);
+                Product(o.w.w, o.c.w, x, p.indexBase, p.cols, 1, hi.w, lo.w);
+                *reinterpret_cast<float4*>(sHi + 4 * v) = hi;
+                *reinterpret_cast<float4*>(sLo + 4 * v) = lo;
+            };
+            constexpr int kVecsPerThread = kTile / 4 / kThreads;
+            Vec4 vv[kVecsPerThread];
+#pragma unroll
+            for (int u = 0; u < kVecsPerThread; ++u) {
+                if (tid + u * kThreads < nvec) {
+                    loadVec(tid + u * kThreads, vv[u]);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < kVecsPerThread; ++u) {
+                if (tid + u * kThreads < nvec) {
+                    useVec(tid + u * kThreads, vv[u]);
+                }
+            }
+            for (int v = tid + kVecsPerThread * kThreads; v < nvec; v += kThreads) {
+                Vec4 vc;
+                loadVec(v, vc);
+                useVec(v, vc);
+            }
+            __syncthreads();
+
+            StagedTile st;
+            st.t = static_cast<int>(t);
+            st.i0 = g.i0;
+            st.i1 = g.i1;
+            st.nr = g.nr;
+            st.nt = g.nt;
+            st.cls = cls;
+            st.hiT = sHi + g.shift;
+            st.loT = sLo + g.shift;
+            st.sOff = sOff;
+            st.sOut = sOut;
+            ReduceTile(st, y, plan, p, scratch);
+        }
+        __syncthreads();  // the stage and the scratch are free
+        if (tid == 0 && tRefill < numTiles) {
+            // Shared-memory writes of the tile above come before the copy engine's writes.
+            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+            const TileGeom r = Geometry(tRefill, refillI0, refillI1, p);
+            IssueTile(r, stage, full + sIdx, colInd, values, plan.rowPtr);
+        }
+    }
+    if (waitedOut) {
+        atomicAdd(waitFailures, 1u);
+    }
+}
+
 // One thread per tile whose first row began in an earlier tile and ends in
 // this one: adds the carry-outs of the tiles the row crossed, oldest first,
 // then the head partial, and writes the row.
@@ -514,7 +841,31 @@ extern "C" void spmv_b200_kernel_do(const void* colInd, const void* values, cons
     }
     const bool vector = p.colIndStride == 1 && p.valuesStride == 1 && p.xStride == 1 &&
                         reinterpret_cast<uintptr_t>(colInd) % 16 == 0 && reinterpret_cast<uintptr_t>(values) % 16 == 0;
-    if (vector) {
+    // ACLSPARSE_SPMV_STREAM=1 selects the persistent bulk-copy kernel.  It needs 16-byte aligned sources
+    // for its copies: the CSR arrays (as the vector path does) and the row offsets inside the plan.
+    static const bool streamEnv = [] {
+        const char* e = std::getenv("ACLSPARSE_SPMV_STREAM");
+        return e != nullptr && e[0] == '1';
+    }();
+    const bool streamed = vector && streamEnv && reinterpret_cast<uintptr_t>(plan.rowPtr) % 16 == 0;
+    if (streamed) {
+        constexpr size_t smem = sizeof(float) * kStreamStages * kStageWords + sizeof(uint64_t) * kStreamStages +
+                                sizeof(ReduceScratch);
+        int device = 0;
+        int sms = 0;
+        if (cudaGetDevice(&device) != cudaSuccess ||
+            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms <= 0) {
+            sms = 148;
+        }
+        cudaFuncSetAttribute(SpmvStreamKernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        const uint32_t resident = static_cast<uint32_t>(sms) * kStreamCtasPerSm;
+        const uint32_t grid = plan.numTiles < resident ? plan.numTiles : resident;
+        auto* waitFailures =
+            reinterpret_cast<uint32_t*>(static_cast<unsigned char*>(workspace) + ACLSP_HEADER_WAIT_FAILURES_OFF);
+        SpmvStreamKernel<<<grid, kThreads, smem, s>>>(
+            static_cast<const int32_t*>(colInd), static_cast<const float*>(values), static_cast<const float*>(x),
+            static_cast<float*>(y), plan, p, waitFailures);
+    } else if (vector) {
         SpmvTileKernel<true><<<plan.numTiles, kThreads, 0, s>>>(
             static_cast<const int32_t*>(colInd), static_cast<const float*>(values), static_cast<const float*>(x),
             static_cast<float*>(y), plan, p);

@@ -92,6 +92,35 @@ def test_benchmark_configs_vs_oracle(name, rows):
         assert np.array_equal(again.view(np.uint32), got.view(np.uint32))
 
 
+def test_both_kernels_give_the_same_bits_and_no_wait_runs_out():
+    """The persistent bulk-copy kernel and the one-CTA-per-tile kernel reduce in the same order: equal bits.
+    The persistent kernel (opt-in) counts bounded waits that ran out in the plan header; the count stays 0."""
+    import subprocess, sys, os
+    code = (
+        "import sys, numpy as np, torch; sys.path.insert(0, %r); sys.path.insert(0, %r)\n"
+        "from gpu_util import SpmvCase\n"
+        "from ops_sparse_b200 import workloads\n"
+        "out = []\n"
+        "for name, rows in (('c1', None), ('c2', 50 ** 3), ('c3', 1 << 16)):\n"
+        "    cfg = workloads.make(name, rows=rows)\n"
+        "    case = SpmvCase(cfg['row_ptr'], cfg['col_ind'], cfg['values'], cfg['x'], cfg['y'])\n"
+        "    got = case.run(cfg['alpha'], cfg['beta'])\n"
+        "    fails = int(case.op.buffer[128:132].view(torch.int32).item())\n"
+        "    assert fails == 0, fails\n"
+        "    out.append(got)\n"
+        "np.save(sys.argv[1], np.concatenate(out))\n"
+    ) % (os.path.dirname(os.path.abspath(__file__)), os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    import tempfile
+    results = {}
+    for mode in ("1", "0"):  # the choice is read once per process
+        with tempfile.TemporaryDirectory() as tmp:
+            path = os.path.join(tmp, "y.npy")
+            env = dict(os.environ, ACLSPARSE_SPMV_STREAM=mode)
+            subprocess.run([sys.executable, "-c", code, path], check=True, env=env, timeout=600)
+            results[mode] = np.load(path)
+    assert np.array_equal(results["1"].view(np.uint32), results["0"].view(np.uint32))
+
+
 def test_plan_metadata_bit_exact():
     """Header, normalised row offsets, tile splits and row bins == the oracle's CPU twin."""
     rng = np.random.default_rng(4)
