@@ -143,8 +143,8 @@ def metric_name(cfg: dict) -> str:
 
 def run_reference(args, cfg):
     """The reference's CPU golden path on the host cores (all threads), same workload and metric."""
-    from oracle import oracle as O
-    threads = O.max_threads()
+    # Every core this process may run on: torchrun exports OMP_NUM_THREADS=1, which must not shrink the baseline.
+    threads = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
     sample = cpu_sample(cfg, args.cpu_rows)
     for _ in range(max(args.warmup, 1)):
         cpu_golden_seconds(sample, threads, 1)
