@@ -349,6 +349,33 @@ def test_row_block_bounds_validation(lib, handle):
     assert lib.aclsparseB200RowBlockBounds(handle, mat, 2, None) == L.INVALID_VALUE
 
 
+def test_mirror_list_validation(lib):
+    """aclsparseB200Dn{Vec,Mat}Set[Multicast]Mirror[s]: at most 7 non-null mirrors, right descriptor kind."""
+    import ctypes
+    vec, mat, csr = make_vec(lib, 8), make_mat(lib, 4, 4, 4), make_csr(lib)
+    seven = (c_void_p * 7)(*[FAKE[i].value for i in range(7)])
+    eight = (c_void_p * 8)(*[FAKE[i % 7].value for i in range(8)])
+    holed = (c_void_p * 2)(FAKE[0].value, None)
+    for setter, multi, good, other in ((lib.aclsparseB200DnVecSetMirrors, lib.aclsparseB200DnVecSetMulticastMirror, vec, mat),
+                                       (lib.aclsparseB200DnMatSetMirrors, lib.aclsparseB200DnMatSetMulticastMirror, mat, vec)):
+        assert setter(good, 7, seven) == L.SUCCESS
+        assert setter(good, 8, eight) == L.INVALID_VALUE
+        assert setter(good, -1, seven) == L.INVALID_VALUE
+        assert setter(good, 2, holed) == L.INVALID_VALUE
+        assert setter(good, 1, None) == L.INVALID_VALUE
+        assert setter(good, 0, None) == L.SUCCESS  # clears the list
+        assert setter(None, 0, None) == L.INVALID_VALUE
+        assert setter(other, 0, None) == L.INVALID_VALUE  # wrong descriptor kind
+        assert setter(csr, 0, None) == L.INVALID_VALUE
+        assert multi(good, FAKE[1]) == L.SUCCESS
+        assert multi(good, None) == L.INVALID_VALUE
+        assert multi(other, FAKE[1]) == L.INVALID_VALUE
+        assert setter(good, 0, None) == L.SUCCESS
+    assert lib.aclsparseDestroyDnVec(vec) == L.SUCCESS
+    assert lib.aclsparseDestroyDnMat(mat) == L.SUCCESS
+    assert lib.aclsparseDestroySpMat(csr) == L.SUCCESS
+
+
 def test_create_destroy_loop(lib):
     """Descriptor churn does not accumulate state (the reference's leak loop, spmv_test.cpp:1710-1738)."""
     for _ in range(2000):
