@@ -570,17 +570,28 @@ __device__ __forceinline__ uint32_t SharedAddress(const void* ptr)
     return static_cast<uint32_t>(__cvta_generic_to_shared(ptr));
 }
 
-__device__ __forceinline__ void BulkLoad(void* smemDst, const void* gmemSrc, uint32_t bytes, uint64_t* bar)
+// The matrix is read once per product: its lines are marked evict-first in L2 so
+// that they do not push x (which every tile gathers from) out of it.
+__device__ __forceinline__ uint64_t EvictFirstPolicy()
 {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(
-                     SharedAddress(smemDst)),
-                 "l"(gmemSrc), "r"(bytes), "r"(SharedAddress(bar))
-                 : "memory");
+    uint64_t policy;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;\n" : "=l"(policy));
+    return policy;
+}
+
+__device__ __forceinline__ void BulkLoad(void* smemDst, const void* gmemSrc, uint32_t bytes, uint64_t* bar,
+                                         uint64_t policy)
+{
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;\n" ::
+            "r"(SharedAddress(smemDst)),
+        "l"(gmemSrc), "r"(bytes), "r"(SharedAddress(bar)), "l"(policy)
+        : "memory");
 }
 
 // Thread 0: announce the bytes of a tile to the stage's barrier and start its copies.
 __device__ __forceinline__ void IssueTile(const TileGeom& g, float* stage, uint64_t* bar, const int32_t* colInd,
-                                          const float* values, const int32_t* rowPtr)
+                                          const float* values, const int32_t* rowPtr, uint64_t policy)
 {
     const uint32_t arrayBytes = g.valid ? 4u * static_cast<uint32_t>(g.copyElems) : 0u;
     const uint32_t offBytes = g.valid ? 4u * static_cast<uint32_t>(g.offWords) : 0u;
@@ -588,11 +599,11 @@ __device__ __forceinline__ void IssueTile(const TileGeom& g, float* stage, uint6
                  "r"(2u * arrayBytes + offBytes)
                  : "memory");
     if (arrayBytes != 0) {
-        BulkLoad(stage, values + g.a0, arrayBytes, bar);
-        BulkLoad(stage + g.span, colInd + g.a0, arrayBytes, bar);
+        BulkLoad(stage, values + g.a0, arrayBytes, bar, policy);
+        BulkLoad(stage + g.span, colInd + g.a0, arrayBytes, bar, policy);
     }
     if (offBytes != 0) {
-        BulkLoad(stage + 2 * g.span, rowPtr + g.offFirst, offBytes, bar);
+        BulkLoad(stage + 2 * g.span, rowPtr + g.offFirst, offBytes, bar, policy);
     }
 }
 
@@ -618,30 +629,32 @@ __device__ __forceinline__ bool WaitStage(uint64_t* bar, uint32_t parity)
     return false;
 }
 
-__global__ void __launch_bounds__(kThreads, kStreamCtasPerSm)
+template <int kStages, int kCtas>
+__global__ void __launch_bounds__(kThreads, kCtas)
 SpmvStreamKernel(const int32_t* __restrict__ colInd, const float* __restrict__ values, const float* __restrict__ x,
                  float* __restrict__ y, SpmvPlanView plan, AclspSpmvParams p, uint32_t* __restrict__ waitFailures)
 {
     extern __shared__ __align__(128) unsigned char smemRaw[];
-    float* stages = reinterpret_cast<float*>(smemRaw);                                   // kStreamStages * kStageWords
-    uint64_t* full = reinterpret_cast<uint64_t*>(stages + kStreamStages * kStageWords);  // kStreamStages barriers
-    ReduceScratch& scratch = *reinterpret_cast<ReduceScratch*>(full + kStreamStages);
+    float* stages = reinterpret_cast<float*>(smemRaw);                                   // kStages * kStageWords
+    uint64_t* full = reinterpret_cast<uint64_t*>(stages + kStages * kStageWords);  // kStages barriers
+    ReduceScratch& scratch = *reinterpret_cast<ReduceScratch*>(full + kStages);
 
     const int tid = threadIdx.x;
     const int nnz = static_cast<int>(p.nnz);
     const uint32_t numTiles = plan.numTiles;
     const uint32_t stride = gridDim.x;
+    const uint64_t policy = EvictFirstPolicy();
 
     if (tid == 0) {
-        for (int sIdx = 0; sIdx < kStreamStages; ++sIdx) {
+        for (int sIdx = 0; sIdx < kStages; ++sIdx) {
             asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(SharedAddress(full + sIdx)) : "memory");
         }
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
         uint32_t t = blockIdx.x;
-        for (int sIdx = 0; sIdx < kStreamStages && t < numTiles; ++sIdx, t += stride) {
+        for (int sIdx = 0; sIdx < kStages && t < numTiles; ++sIdx, t += stride) {
             const TileGeom g = Geometry(t, plan.tileRow[t], plan.tileRow[t + 1], p);
-            IssueTile(g, stages + sIdx * kStageWords, full + sIdx, colInd, values, plan.rowPtr);
+            IssueTile(g, stages + sIdx * kStageWords, full + sIdx, colInd, values, plan.rowPtr, policy);
         }
     }
     __syncthreads();
@@ -656,8 +669,8 @@ SpmvStreamKernel(const int32_t* __restrict__ colInd, const float* __restrict__ v
     }
     bool waitedOut = false;
     for (uint32_t it = 0; t < numTiles; ++it, t += stride) {
-        const int sIdx = static_cast<int>(it % kStreamStages);
-        const uint32_t parity = (it / kStreamStages) & 1u;
+        const int sIdx = static_cast<int>(it % kStages);
+        const uint32_t parity = (it / kStages) & 1u;
         float* stage = stages + sIdx * kStageWords;
         const TileGeom g = Geometry(t, nextI0, nextI1, p);
         const int cls = nextCls;
@@ -668,7 +681,7 @@ SpmvStreamKernel(const int32_t* __restrict__ colInd, const float* __restrict__ v
             nextCls = plan.tileClass[tNext];
         }
         // Thread 0 refills this stage after the tile: its split points are fetched now.
-        const uint32_t tRefill = t + kStreamStages * stride;
+        const uint32_t tRefill = t + kStages * stride;
         int refillI0 = 0, refillI1 = 0;
         if (tid == 0 && tRefill < numTiles) {
             refillI0 = plan.tileRow[tRefill];
@@ -770,7 +783,7 @@ SpmvStreamKernel(const int32_t* __restrict__ colInd, const float* __restrict__ v
             // Shared-memory writes of the tile above come before the copy engine's writes.
             asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
             const TileGeom r = Geometry(tRefill, refillI0, refillI1, p);
-            IssueTile(r, stage, full + sIdx, colInd, values, plan.rowPtr);
+            IssueTile(r, stage, full + sIdx, colInd, values, plan.rowPtr, policy);
         }
     }
     if (waitedOut) {
@@ -849,22 +862,31 @@ extern "C" void spmv_b200_kernel_do(const void* colInd, const void* values, cons
     }();
     const bool streamed = vector && streamEnv && reinterpret_cast<uintptr_t>(plan.rowPtr) % 16 == 0;
     if (streamed) {
-        constexpr size_t smem = sizeof(float) * kStreamStages * kStageWords + sizeof(uint64_t) * kStreamStages +
-                                sizeof(ReduceScratch);
         int device = 0;
         int sms = 0;
         if (cudaGetDevice(&device) != cudaSuccess ||
             cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms <= 0) {
             sms = 148;
         }
-        cudaFuncSetAttribute(SpmvStreamKernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-        const uint32_t resident = static_cast<uint32_t>(sms) * kStreamCtasPerSm;
-        const uint32_t grid = plan.numTiles < resident ? plan.numTiles : resident;
         auto* waitFailures =
             reinterpret_cast<uint32_t*>(static_cast<unsigned char*>(workspace) + ACLSP_HEADER_WAIT_FAILURES_OFF);
-        SpmvStreamKernel<<<grid, kThreads, smem, s>>>(
-            static_cast<const int32_t*>(colInd), static_cast<const float*>(values), static_cast<const float*>(x),
-            static_cast<float*>(y), plan, p, waitFailures);
+        auto launch = [&](auto kernel, int stages, int ctas) {
+            const size_t smem = sizeof(float) * stages * kStageWords + sizeof(uint64_t) * stages + sizeof(ReduceScratch);
+            cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+            const uint32_t resident = static_cast<uint32_t>(sms) * ctas;
+            const uint32_t grid = plan.numTiles < resident ? plan.numTiles : resident;
+            kernel<<<grid, kThreads, smem, s>>>(static_cast<const int32_t*>(colInd), static_cast<const float*>(values),
+                                                static_cast<const float*>(x), static_cast<float*>(y), plan, p,
+                                                waitFailures);
+        };
+        static const int cfgEnv = [] { const char* e = std::getenv("ACLSPARSE_DEBUG_STREAM_CFG"); return e ? atoi(e) : 0; }();
+        if (cfgEnv == 1) {
+            launch(SpmvStreamKernel<2, 5>, 2, 5);
+        } else if (cfgEnv == 2) {
+            launch(SpmvStreamKernel<2, 6>, 2, 6);
+        } else {
+            launch(SpmvStreamKernel<kStreamStages, kStreamCtasPerSm>, kStreamStages, kStreamCtasPerSm);
+        }
     } else if (vector) {
         SpmvTileKernel<true><<<plan.numTiles, kThreads, 0, s>>>(
             static_cast<const int32_t*>(colInd), static_cast<const float*>(values), static_cast<const float*>(x),

@@ -86,3 +86,17 @@ def test_two_rank_gather_reassembles_the_product():
     results = mgr.dict()
     mp.spawn(_worker, args=(2, port, results), nprocs=2, join=True)
     assert dict(results) == {0: (0, 0, 1 << 12, (1 << 10, 128)), 1: (0, 0, 1 << 12, (1 << 10, 128))}
+
+
+def test_reassembly_modes_off_gpu_and_single_rank():
+    """Without CUDA every reassembly mode resolves to the all-gather; one rank returns its block untouched."""
+    cfg = workloads.make("c1")
+    for mode in ("multicast", "fused", "push", "nccl"):
+        op = sharded.ShardedSpMV(cfg, 0, 1, torch.device("cpu"), local_product=_spmv_stand_in, gather=mode)
+        assert op.gather_mode == "nccl"
+        assert not op.capture(1.0, 0.0)         # nothing to record without the CUDA operators
+        op.reassemble_in_kernel(True)           # and nothing to register
+        y = op.step(cfg["alpha"], cfg["beta"])
+        assert y.data_ptr() == op.y_local.data_ptr() and y.shape == (cfg["rows"],)
+        truth = O.spmv_f64(cfg["row_ptr"], cfg["col_ind"], cfg["values"], cfg["x"], cfg["y"], cfg["alpha"], cfg["beta"])
+        assert O.check_tolerance(y.numpy(), truth)[0] == 0
