@@ -321,10 +321,12 @@ def run_ours(args, cfg):
     flop = workloads.flops(cfg)
     abytes = workloads.algorithmic_bytes(cfg)
     achieved = abytes / (k_ms * 1e-3) / 1e9 if k_ms else None
-    # DRAM read + write bytes per launch from the ncu capture of the 1 M-row stencil (225.04 MB for 223.71 MB
-    # algorithmic), scaled by the non-zeros; SpMV traffic is proportional to them.  No capture scales to the
-    # other workloads' full sizes (the SpMM traffic depends on the ratio of B to L2), so theirs stays null.
-    traffic = int(abytes * 225.04 / 223.71) if cfg["name"] == "c2" and cfg["rows"] == 4096000 and world == 1 else None
+    # DRAM read + write bytes per launch, from the ncu captures of the 1 M-row cases of the same kernel
+    # (stencil: 225.04 MB for 223.71 MB algorithmic; power-law: 273.9 MB for 272.2 MB), scaled by the algorithmic
+    # bytes: SpMV traffic is proportional to them.  The SpMM traffic depends on the ratio of B to L2 and no
+    # small capture scales to the full sizes, so it stays null.
+    ratio = {"c2": 225.04 / 223.71, "c3": 273.9 / 272.24}.get(cfg["name"])
+    traffic = int(abytes * ratio) if ratio and args.rows is None and world == 1 else None
     line = {
         "metric": metric_name(cfg), "value": flop / (ms_step * 1e-3) / 1e9, "unit": "GFLOP/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
