@@ -4,22 +4,33 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2] [--impl ours|reference]
 
 One "step" is one product over one batch of synthetic input: y = alpha*A*x + beta*y (or the SpMM
-equivalent) with A resident on the device(s).  The default workload is c2, the 27-point stencil on a
+equivalent) with A resident on the device(s).  The headline workload is c2, the 27-point stencil on a
 160^3 grid (4 096 000 rows, 109 215 352 non-zeros), the configuration the headline metric is quoted
-on; c1/c3/c4/c5 select the other configurations of ops_sparse_b200/workloads.py.
+on.  The same run then measures the other configurations of ops_sparse_b200/workloads.py (c1, c3, c4,
+c5 at one GPU; c3 and c4 at several) the same way and reports them under "configs" in the same line;
+--configs picks another list, --configs none skips them.
 
 At N GPUs (launched by torchrun, one rank per GPU) the same matrix is row-block sharded by nnz, x / B
-is replicated and every step ends with the all-gather that reassembles y / C on every rank, so total
-work is fixed ("strong" scaling).  Timing: W warm-up steps, then K steps between barriers and device
+is replicated and every step ends with the reassembly of y / C on every rank, so total work is fixed
+("strong" scaling).  Timing: W warm-up steps, then K steps between barriers and device
 synchronisations, each step bracketed by CUDA events on the launching stream; the reported time is
 the maximum over ranks.  The matrix alone (0.9 - 5.7 GB) is far larger than the 126 MB L2, so every
-step streams it from HBM again.
+step streams it from HBM again (c1, 2 MB, is L2-resident by nature and is reported as such).
+
+Every rank compares the WHOLE result it holds (all rows of the reassembled y / C) with the oracle's
+fp64 truth, once before the timed steps and once after the last of them; the line reports the rows
+checked, the number of ranks that checked and the largest violation count over ranks and checks.
 
 Rank 0 prints one JSON line.  Keys beyond the usual ones:
-  roofline      SpMV/SpMM kernels of one product: algorithmic bytes (the CSR arrays, x or B, y or C,
-                each once) / event-timed duration, against the measured HBM copy bandwidth
-  e2e           the same product driven from HOST vectors through the C API: pinned x (or B) is copied
-                to the device, the product runs, y (or C) is copied back, all inside the timed region
+  roofline      the product kernels of one step: algorithmic bytes (the CSR arrays, x or B, y or C,
+                each once) / event-timed duration, against the measured HBM copy bandwidth.  At one
+                GPU the step is exactly those kernels (one graph replay); at several GPUs they are
+                timed as their own graph replay with the reassembly switched off
+  e2e           the same product driven from HOST buffers: each rank copies its share of x (or B) from
+                pinned host memory, the shares are all-gathered into the replicas over NVLink, the
+                sharded product step runs, and each rank copies its own row block of y (or C) back to
+                pinned host memory, all inside the timed region; at one GPU that is the plain
+                aclsparseSpMV / aclsparseSpMM call between two copies
   cpu_baseline  the test oracle's restatement of the reference's host golden, timed on one host core
                 (the way the reference's tests time it) on the same inputs
   --impl reference times that CPU golden with all host threads instead of the GPU path.
@@ -27,6 +38,7 @@ Rank 0 prints one JSON line.  Keys beyond the usual ones:
 from __future__ import annotations
 
 import argparse
+import gc
 import json
 import os
 import subprocess
@@ -42,6 +54,11 @@ sys.path.insert(0, ROOT)
 from ops_sparse_b200 import workloads  # noqa: E402
 
 FALLBACK_HBM_GBS = 6650.0
+
+# DRAM read + write bytes per algorithmic byte, from ncu captures of the kernels named (profiles/):
+# SpMV traffic is proportional to the algorithmic bytes, so a 1 M-row capture scales; the SpMM figures
+# are from one full-size launch each.
+TRAFFIC_RATIO = {}
 
 
 def measured_peak():
@@ -105,6 +122,11 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
+def host_threads() -> int:
+    """Every core this process may run on: torchrun exports OMP_NUM_THREADS=1, which must not shrink a CPU leg."""
+    return len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+
+
 def cpu_golden_seconds(cfg: dict, threads: int, repeats: int) -> float:
     """Average seconds of one product by the oracle's restatement of the reference's host golden."""
     from oracle import oracle as O
@@ -141,10 +163,20 @@ def metric_name(cfg: dict) -> str:
     return "spmv_gflops" if cfg["kind"] == "spmv" else "spmm_gflops"
 
 
+def describe(cfg: dict) -> str:
+    text = {
+        "c1": "c1: CSR SpMV fp32 16384^2, Poisson(16) rows clamped to [1,64], alpha=1 beta=0",
+        "c2": "c2: CSR SpMV fp32, 27-point stencil on a 160^3 grid, alpha=1 beta=0",
+        "c3": "c3: CSR SpMV fp32 power-law 4194304^2, Zipf(2.0) rows mean 32 cap 200000, alpha=1.5 beta=0.5",
+        "c4": "c4: CSR SpMM fp32 1048576^2 Poisson(16) rows, B 1048576x128 row-major, alpha=1 beta=0",
+        "c5": "c5: CSR SpMM fp32 power-law 8388608^2, Zipf(2.1) rows mean 20 cap 500000, B 8388608x64",
+    }[cfg["name"]]
+    return f"{text} ({cfg['rows']} rows, {cfg['nnz']} nnz)"
+
+
 def run_reference(args, cfg):
     """The reference's CPU golden path on the host cores (all threads), same workload and metric."""
-    # Every core this process may run on: torchrun exports OMP_NUM_THREADS=1, which must not shrink the baseline.
-    threads = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    threads = host_threads()
     sample = cpu_sample(cfg, args.cpu_rows)
     for _ in range(max(args.warmup, 1)):
         cpu_golden_seconds(sample, threads, 1)
@@ -165,30 +197,83 @@ def run_reference(args, cfg):
     print(json.dumps(line))
 
 
-def describe(cfg: dict) -> str:
-    text = {
-        "c1": "c1: CSR SpMV fp32 16384^2, Poisson(16) rows clamped to [1,64], alpha=1 beta=0",
-        "c2": "c2: CSR SpMV fp32, 27-point stencil on a 160^3 grid, alpha=1 beta=0",
-        "c3": "c3: CSR SpMV fp32 power-law 4194304^2, Zipf(2.0) rows mean 32 cap 200000, alpha=1.5 beta=0.5",
-        "c4": "c4: CSR SpMM fp32 1048576^2 Poisson(16) rows, B 1048576x128 row-major, alpha=1 beta=0",
-        "c5": "c5: CSR SpMM fp32 power-law 8388608^2, Zipf(2.1) rows mean 20 cap 500000, B 8388608x64",
-    }[cfg["name"]]
-    return f"{text} ({cfg['rows']} rows, {cfg['nnz']} nnz)"
+class Context:
+    """Process group, device and the small collectives the measurement needs."""
+
+    def __init__(self, args):
+        import torch
+        import torch.distributed as dist
+
+        from ops_sparse_b200 import _lib as L
+        from ops_sparse_b200 import sharded
+
+        if not torch.cuda.is_available():
+            raise SystemExit("bench.py needs a CUDA device: the operators have no CPU implementation")
+        L.lib()  # fails loudly when libops_sparse.so is missing
+        self.torch, self.dist, self.sharded = torch, dist, sharded
+        self.rank, self.world, self.device = sharded.init_process_group_from_env()
+        if self.world != args.gpus:
+            raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={self.world}: launch with torchrun --nproc-per-node N")
+
+    def barrier(self):
+        self.torch.cuda.synchronize()
+        if self.world > 1:
+            self.dist.barrier()
+        self.torch.cuda.synchronize()
+
+    def max_over_ranks(self, v: float) -> float:
+        if self.world == 1:
+            return v
+        t = self.torch.tensor([v], dtype=self.torch.float64, device=self.device)
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def sum_over_ranks(self, v: float) -> float:
+        if self.world == 1:
+            return v
+        t = self.torch.tensor([v], dtype=self.torch.float64, device=self.device)
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.SUM)
+        return float(t.item())
 
 
-def run_ours(args, cfg):
-    import torch
-    import torch.distributed as dist
+def check_whole_result(ctx: Context, cfg: dict, full, alpha: float, beta: float) -> dict:
+    """This rank's whole reassembled y / C against the oracle's fp64 truth; reduced over ranks."""
+    from oracle import oracle as O
+    threads = max(1, host_threads() // ctx.world)
+    rows = cfg["rows"]
+    bad, max_abs, max_rel = 0, 0.0, 0.0
+    if cfg["kind"] == "spmv":
+        truth = O.spmv_f64(cfg["row_ptr"], cfg["col_ind"], cfg["values"], cfg["x"], cfg["y"], alpha, beta,
+                           threads=threads)
+        bad, max_abs, max_rel = O.check_tolerance(full[:rows].cpu().numpy(), truth)
+    else:
+        n = cfg["n"]
+        chunk = max(1, (1 << 27) // n)  # a GiB of fp64 truth at a time
+        for r0 in range(0, rows, chunk):
+            r1 = min(rows, r0 + chunk)
+            truth = O.spmm_f64(cfg["row_ptr"], cfg["col_ind"], cfg["values"], cfg["b"], n, cfg["c"], n, n,
+                               cfg["cols"], alpha, beta, row_begin=r0, row_end=r1, threads=threads)
+            b, a, r = O.check_tolerance(full[r0:r1].cpu().numpy(), truth)
+            bad, max_abs, max_rel = bad + b, max(max_abs, a), max(max_rel, r)
+    return {"rows_checked": rows, "violations": int(ctx.max_over_ranks(float(bad))),
+            "ranks_checked": int(ctx.sum_over_ranks(1.0)), "max_abs_err": ctx.max_over_ranks(max_abs),
+            "max_rel_err": ctx.max_over_ranks(max_rel), "rtol": 1e-5, "atol": 1e-6}
 
-    from ops_sparse_b200 import _lib as L
-    from ops_sparse_b200 import sharded
 
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device: the operators have no CPU implementation")
-    L.lib()  # fails loudly when libops_sparse.so is missing
-    rank, world, device = sharded.init_process_group_from_env()
-    if world != args.gpus:
-        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torchrun --nproc-per-node N")
+def merge_checks(a: dict, b: dict) -> dict:
+    out = dict(a)
+    out["violations"] = max(a["violations"], b["violations"])
+    out["max_abs_err"] = max(a["max_abs_err"], b["max_abs_err"])
+    out["max_rel_err"] = max(a["max_rel_err"], b["max_rel_err"])
+    out["ranks_checked"] = min(a["ranks_checked"], b["ranks_checked"])
+    out["checks"] = "whole result on every rank, before the timed steps and after the last of them"
+    return out
+
+
+def measure(ctx: Context, args, cfg: dict, steps: int, warmup: int, min_warm_seconds: float) -> dict:
+    """Everything that is reported about one configuration (see the module docstring)."""
+    torch, dist, sharded = ctx.torch, ctx.dist, ctx.sharded
+    rank, world, device = ctx.rank, ctx.world, ctx.device
     spmv = cfg["kind"] == "spmv"
     op = (sharded.ShardedSpMV if spmv else sharded.ShardedSpMM)(cfg, rank, world, device, gather=args.gather)
     alpha, beta = cfg["alpha"], cfg["beta"]
@@ -196,170 +281,194 @@ def run_ours(args, cfg):
     local0 = out0[op.r0:op.r1].to(device)
     local = op.y_local if spmv else op.c_local
 
-    def barrier():
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
+    def reset_output():
+        if beta != 0.0:
+            local.copy_(local0)  # outside the event pairs: keeps the input of every step identical
 
-    def max_over_ranks(v: float) -> float:
-        if world == 1:
-            return v
-        t = torch.tensor([v], dtype=torch.float64, device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
-
-    # ---- correctness of the very data that is timed: one step against the oracle (rank 0's rows)
+    # ---- correctness of the very data that is timed: the whole result, on every rank
+    reset_output()
     full = op.step(alpha, beta)
     torch.cuda.synchronize()
-    check = None
-    if rank == 0 and not args.no_check:
-        from oracle import oracle as O
-        rows = min(cfg["rows"], args.check_rows)
-        if spmv:
-            sub = cpu_sample(cfg, rows)
-            truth = O.spmv_f64(sub["row_ptr"], sub["col_ind"], sub["values"], cfg["x"], sub["y"], alpha, beta,
-                               threads=O.max_threads())
-            bad, max_abs, max_rel = O.check_tolerance(full[:rows].cpu().numpy(), truth)
-        else:
-            n = cfg["n"]
-            truth = O.spmm_f64(cfg["row_ptr"], cfg["col_ind"], cfg["values"], cfg["b"], n, cfg["c"], n, n,
-                               cfg["cols"], alpha, beta, row_begin=0, row_end=rows, threads=O.max_threads())
-            bad, max_abs, max_rel = O.check_tolerance(full[:rows].cpu().numpy(), truth)
-        check = {"rows_checked": rows, "violations": bad, "max_abs_err": max_abs, "max_rel_err": max_rel,
-                 "rtol": 1e-5, "atol": 1e-6}
+    check = None if args.no_check else check_whole_result(ctx, cfg, full, alpha, beta)
     del full
-    barrier()  # the next step overwrites the buffers rank 0 has just read
+    ctx.barrier()  # the next step overwrites the buffers the ranks have just read
     graphed = (not args.no_graph) and op.capture(alpha, beta)
 
     # ---- device-resident steps
-    # nvidia-smi needs about a second to deliver its first sample, far longer than a few steps take:
-    # sampling starts here, warm-up keeps the GPU under the same load until samples arrive, and
-    # the sampler runs on through the timed steps and the kernel-only and host-buffer loops.
-    sampler = ClockSampler(device.index or 0)
-    if rank == 0:
-        sampler.start()
-    warm_until = time.perf_counter() + 1.5
+    # nvidia-smi needs about a second to deliver its first sample: warm-up keeps the GPU under the same
+    # load at least that long where a clock sample is wanted for this configuration.
+    warm_until = time.perf_counter() + min_warm_seconds
     done = 0
-    while done < args.warmup or (rank == 0 and world == 1 and time.perf_counter() < warm_until):
-        if beta != 0.0:
-            local.copy_(local0)
+    while done < warmup or (rank == 0 and world == 1 and time.perf_counter() < warm_until):
+        reset_output()
         op.step(alpha, beta)
         done += 1
         if done % 16 == 0:
             torch.cuda.synchronize()
-    barrier()
-    starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
-    ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
-    for i in range(args.steps):
-        if beta != 0.0:
-            local.copy_(local0)  # outside the event pair: keeps the input of every step identical
+    ctx.barrier()
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+    ends = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+    for i in range(steps):
+        reset_output()
         starts[i].record()
         op.step(alpha, beta)
         ends[i].record()
-    barrier()
+    ctx.barrier()
     per_step = [s.elapsed_time(e) for s, e in zip(starts, ends)]
-    ms_total = max_over_ranks(float(sum(per_step)))
-    ms_step = ms_total / args.steps
+    ms_step = ctx.max_over_ranks(float(sum(per_step))) / steps
 
-    # ---- the product kernels alone (no reassembly: mirrors of the output cleared), for the roofline
-    k_ms = None
-    op.reassemble_in_kernel(False)
-    if hasattr(op, "op") and op.r1 > op.r0:
-        ks = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
-        ke = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
-        for i in range(args.steps):
-            if beta != 0.0:
-                local.copy_(local0)
-            ks[i].record()
-            op.op(alpha, beta)
-            ke[i].record()
+    # ---- the whole result once more, after the last timed (graph-replayed) step
+    if check is not None:
+        reset_output()
+        full = op.step(alpha, beta)
         torch.cuda.synchronize()
-        k_ms = float(np.mean([s.elapsed_time(e) for s, e in zip(ks, ke)]))
-    k_ms = max_over_ranks(k_ms if k_ms is not None else 0.0)
-    op.reassemble_in_kernel(True)
+        check = merge_checks(check, check_whole_result(ctx, cfg, full, alpha, beta))
+        del full
+        ctx.barrier()
+
+    # ---- the product kernels alone, for the roofline.  At one GPU the step is exactly them; at several
+    # GPUs they are replayed as a graph of their own with the reassembly (output mirrors) switched off.
+    k_ms = ms_step
+    if world > 1:
+        k_ms = 0.0
+        op.reassemble_in_kernel(False)
+        if op.r1 > op.r0:
+            replay = op.capture_product(alpha, beta) if not args.no_graph else None
+            run = replay if replay is not None else (lambda: op.op(alpha, beta))
+            for _ in range(3):
+                run()
+            ks = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+            ke = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+            for i in range(steps):
+                reset_output()
+                ks[i].record()
+                run()
+                ke[i].record()
+            torch.cuda.synchronize()
+            k_ms = float(np.mean([s.elapsed_time(e) for s, e in zip(ks, ke)]))
+        k_ms = ctx.max_over_ranks(k_ms)
+        op.reassemble_in_kernel(True)
 
     # ---- end to end from host buffers through the public API
-    # Every rank copies x (or B) from pinned host memory, takes part in the step and copies the whole
-    # reassembled y (or C) back; at one GPU the step is the plain aclsparseSpMV / SpMM call.
     e2e = None
     try:
-        inp = torch.from_numpy(cfg["x"] if spmv else cfg["b"]).pin_memory()
-        host_out = torch.empty_like(out0).pin_memory()
-        dev_in = op.x if spmv else op.b
-        e_steps = max(1, min(args.steps, 5 if not spmv else args.steps))
-        barrier()
+        host_in = op.pinned_input_share(cfg)
+        host_out = torch.empty_like(out0[op.r0:op.r1]).pin_memory()
+        e_steps = max(1, min(steps, 3 if not spmv else steps))
+        ctx.barrier()
         for it in range(1 + e_steps):
             if it == 1:
-                barrier()
+                ctx.barrier()
                 t0 = torch.cuda.Event(enable_timing=True)
                 t1 = torch.cuda.Event(enable_timing=True)
                 t0.record()
-            dev_in.copy_(inp, non_blocking=True)
-            if beta != 0.0:
-                local.copy_(local0)
+            op.load_input_share(host_in)
+            reset_output()
             result = op.step(alpha, beta)
-            host_out.copy_(result.view(host_out.shape), non_blocking=True)
+            host_out.copy_(result[op.r0:op.r1].view(host_out.shape), non_blocking=True)
         t1.record()
-        barrier()
-        e_ms = max_over_ranks(t0.elapsed_time(t1)) / e_steps
-        e2e = {"value": workloads.flops(cfg) / (e_ms * 1e-3) / 1e9, "unit": "GFLOP/s",
-               "h2d_bytes_per_step": int(inp.numel() * 4) * world, "d2h_bytes_per_step": int(host_out.numel() * 4) * world,
-               "ms_per_step": e_ms, "steps": e_steps,
-               "what": "per rank: pinned host x (or B) -> device, the sharded product step, whole y (or C) -> pinned host; "
-                       "A resident; bytes are summed over ranks"}
+        ctx.barrier()
+        e_ms = ctx.max_over_ranks(t0.elapsed_time(t1)) / e_steps
+        h2d = int(ctx.sum_over_ranks(float(host_in.numel() * 4)))
+        d2h = int(ctx.sum_over_ranks(float(host_out.numel() * 4)))
+        e2e = {"value": workloads.flops(cfg) / (e_ms * 1e-3) / 1e9, "unit": "GFLOP/s", "h2d_bytes_per_step": h2d,
+               "d2h_bytes_per_step": d2h, "ms_per_step": e_ms, "steps": e_steps,
+               "what": "per rank: its share of x (or B) pinned host -> device, all-gather of the shares into the "
+                       "replicas, the sharded product step, its own row block of y (or C) -> pinned host; A "
+                       "resident; bytes are summed over ranks"}
+        del host_in, host_out
     except (RuntimeError, ValueError, TypeError) as err:  # the same on every rank: none is left waiting
         e2e = None
-        print(f"[bench] end-to-end leg failed: {err!r}", file=sys.stderr)
+        print(f"[bench] end-to-end leg of {cfg['name']} failed: {err!r}", file=sys.stderr)
 
-    clocks = sampler.stop() if rank == 0 else None
-    if world > 1:
-        dist.barrier()  # last collective: every rank reaches it before any rank leaves
-    if rank != 0:
-        return
     peak, peak_kind = measured_peak()
     flop = workloads.flops(cfg)
     abytes = workloads.algorithmic_bytes(cfg)
     achieved = abytes / (k_ms * 1e-3) / 1e9 if k_ms else None
-    # DRAM read + write bytes per launch, from the ncu captures of the 1 M-row cases of the same kernel
-    # (stencil: 225.04 MB for 223.71 MB algorithmic; power-law: 273.9 MB for 272.2 MB), scaled by the algorithmic
-    # bytes: SpMV traffic is proportional to them.  The SpMM traffic depends on the ratio of B to L2 and no
-    # small capture scales to the full sizes, so it stays null.
-    ratio = {"c2": 225.04 / 223.71, "c3": 273.9 / 272.24}.get(cfg["name"])
-    traffic = int(abytes * ratio) if ratio and args.rows is None and world == 1 else None
-    line = {
-        "metric": metric_name(cfg), "value": flop / (ms_step * 1e-3) / 1e9, "unit": "GFLOP/s", "n_gpus": world,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
-        "scaling": "strong", "vs_baseline": None, "dtype": "f32 data, f64 accumulate" if spmv else "f32",
-        "data": "synthetic",
+    ratio = TRAFFIC_RATIO.get(cfg["name"])
+    traffic = int(abytes * ratio) if ratio and args.rows is None else None
+    launches = op.launches_per_step()
+    result = {
+        "metric": metric_name(cfg), "value": flop / (ms_step * 1e-3) / 1e9, "unit": "GFLOP/s",
+        "ms_per_step": ms_step, "steps": steps, "warmup": done,
+        "dtype": "f32 data, f64 accumulate",
+        "algorithm": op.algorithm,
         "config": {"workload": describe(cfg), "sharding": f"row blocks by nnz over {world} GPU(s), x/B replicated, "
                    f"reassembly of y/C inside the step ({op.gather_mode if world > 1 else 'none at 1 GPU'})",
-                   "launch": "one CUDA graph replay per step" if graphed else "kernel by kernel", "l2": "inputs larger than L2 (matrix streamed from HBM every "
-                   "step); no flush", "per_step_ms_min_median_max": [float(np.min(per_step)),
-                                                                     float(np.median(per_step)),
-                                                                     float(np.max(per_step))]},
-        "clocks": clocks,
-        # tile kernel + carry fix-up kernel (+ the push kernel at N > 1) per timed step and rank
-        "gpu_launches": (3 if world > 1 and op.gather_mode == "push" else 2) * args.steps,
+                   "launch": "one CUDA graph replay per step" if graphed else "kernel by kernel",
+                   "l2": ("the whole problem fits L2: no flush, reported as L2-resident" if abytes < 100e6 else
+                          "inputs larger than L2 (matrix streamed from HBM every step); no flush"),
+                   "per_step_ms_min_median_max": [float(np.min(per_step)), float(np.median(per_step)),
+                                                  float(np.max(per_step))]},
+        "gpu_launches": launches * steps,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak * world, "peak_per_gpu": peak, "unit": "GB/s",
-                     "frac": achieved / (peak * world) if achieved else None, "traffic": traffic, "peak_kind": peak_kind,
-                     "algorithmic_bytes_per_launch": abytes, "kernel_ms": k_ms,
+                     "frac": achieved / (peak * world) if achieved else None, "traffic": traffic,
+                     "peak_kind": peak_kind, "algorithmic_bytes_per_launch": abytes, "kernel_ms": k_ms,
                      "frac_of_nominal_8000": achieved / (8000.0 * world) if achieved else None,
-                     "kernels": "SpmvTileKernel + SpmvCarryFixupKernel" if spmv else
-                                "SpmmTileKernel + SpmmCarryFixupKernel",
+                     "kernels": op.kernel_names,
                      "hbm_gbs_at_step_time": abytes / (ms_step * 1e-3) / 1e9},
         "check": check,
     }
+    if not spmv:
+        result["roofline"]["gather_bytes"] = 4 * cfg["nnz"] * cfg["n"]
     if e2e is not None:
-        line["e2e"] = e2e
-    if world == 1 and not args.no_cpu:
+        result["e2e"] = e2e
+    op.close()
+    del op, local0, out0
+    gc.collect()
+    torch.cuda.empty_cache()
+    return result
+
+
+def run_ours(args):
+    ctx = Context(args)
+    rank, world = ctx.rank, ctx.world
+    sampler = ClockSampler(ctx.device.index or 0)
+    if rank == 0:
+        sampler.start()
+    cfg = workloads.make(args.workload, rows=args.rows)
+    head = measure(ctx, args, cfg, args.steps, args.warmup, 1.5)
+    clocks = sampler.stop() if rank == 0 else None
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
         sample = cpu_sample(cfg, args.cpu_rows)
         secs = cpu_golden_seconds(sample, 1, args.cpu_repeats)
-        line["cpu_baseline"] = {
-            "value": workloads.flops(sample) / secs / 1e9, "unit": "GFLOP/s", "cores": 1, "kind": "port",
-            "sample": f"{sample['rows']} of {cfg['rows']} rows ({sample['nnz']} non-zeros) x {args.cpu_repeats} "
-                      "passes, single thread, the reference's host golden restated in oracle/oracle.c",
-            "host_cores_available": os.cpu_count()}
+        cpu = {"value": workloads.flops(sample) / secs / 1e9, "unit": "GFLOP/s", "cores": 1, "kind": "port",
+               "sample": f"{sample['rows']} of {cfg['rows']} rows ({sample['nnz']} non-zeros) x {args.cpu_repeats} "
+                         "passes, single thread, the reference's host golden restated in oracle/oracle.c",
+               "host_cores_available": os.cpu_count()}
+    del cfg
+    gc.collect()
+
+    names = args.configs
+    if names is None:
+        names = ["c1", "c3", "c4", "c5"] if world == 1 else ["c3", "c4"]
+    configs = {}
+    for name in names:
+        if name == args.workload and args.rows is None:
+            continue
+        other = workloads.make(name, rows=args.rows if args.rows is not None and name != "c1" else None)
+        steps = args.steps if other["kind"] == "spmv" else max(3, min(args.steps, 10))
+        configs[name] = measure(ctx, args, other, steps, max(3, args.warmup), 0.0)
+        del other
+        gc.collect()
+
+    if world > 1:
+        ctx.dist.barrier()  # last collective: every rank reaches it before any rank leaves
+    if rank != 0:
+        return
+    line = {"metric": head["metric"], "value": head["value"], "unit": head["unit"], "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": head["ms_per_step"], "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": head["dtype"], "data": "synthetic",
+            "algorithm": head["algorithm"], "config": head["config"], "clocks": clocks,
+            "gpu_launches": head["gpu_launches"], "roofline": head["roofline"], "check": head["check"]}
+    if "e2e" in head:
+        line["e2e"] = head["e2e"]
+    if cpu is not None:
+        line["cpu_baseline"] = cpu
+    if configs:
+        line["configs"] = configs
     print(json.dumps(line))
 
 
@@ -370,8 +479,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2", choices=["c1", "c2", "c3", "c4", "c5"])
+    ap.add_argument("--configs", default=None,
+                    help="comma-separated further configurations measured in the same run and reported under "
+                    "'configs' (default: c1,c3,c4,c5 at one GPU, c3,c4 at several); 'none' for none")
     ap.add_argument("--rows", type=int, default=None, help="row count override (smaller case of the same shape)")
-    ap.add_argument("--check-rows", type=int, default=1 << 20, help="rows compared with the oracle before timing")
     ap.add_argument("--cpu-rows", type=int, default=1 << 22, help="row block the CPU baseline runs on")
     ap.add_argument("--cpu-repeats", type=int, default=3)
     ap.add_argument("--gather", default="multicast", choices=["multicast", "fused", "push", "nccl"],
@@ -384,18 +495,18 @@ def main():
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.configs is not None:
+        args.configs = [] if args.configs.lower() in ("none", "") else [c.strip() for c in args.configs.split(",")]
 
-    if args.impl == "reference" and int(os.environ.get("RANK", "0")) != 0:
-        return  # the CPU arm runs on rank 0 only
-    cfg = workloads.make(args.workload, rows=args.rows)
     if args.impl == "reference":
-        run_reference(args, cfg)
-    else:
-        run_ours(args, cfg)
-    if args.impl == "ours":
-        import torch.distributed as dist
-        if dist.is_initialized():
-            dist.destroy_process_group()
+        if int(os.environ.get("RANK", "0")) != 0:
+            return  # the CPU arm runs on rank 0 only
+        run_reference(args, workloads.make(args.workload, rows=args.rows))
+        return
+    run_ours(args)
+    import torch.distributed as dist
+    if dist.is_initialized():
+        dist.destroy_process_group()
 
 
 if __name__ == "__main__":

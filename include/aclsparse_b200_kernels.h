@@ -49,7 +49,13 @@ typedef struct AclspSpmvParams {
     uint32_t numMirrors;     /* 0: y only */
     uint32_t mirrorMulticast;
     int64_t mirrorDelta[ACLSP_MAX_MIRRORS];
+    /* Longest row of the matrix as the preprocessing pass recorded it in the plan header, when the host
+     * has learnt it (an asynchronous copy to pinned memory), else ACLSP_MAX_ROW_LEN_UNKNOWN: then both
+     * SpMV kernels are launched and decide by the plan header which of them computes. */
+    uint32_t maxRowLenHint;
 } AclspSpmvParams;
+
+#define ACLSP_MAX_ROW_LEN_UNKNOWN 0xFFFFFFFFu
 
 /* Per-launch parameters of the SpMM kernels.  Counterpart of the reference's
  * SpmmTilingWireV1 (sparse/spmm/arch35/spmm_tiling_wire.h:23-74). */
@@ -62,7 +68,7 @@ typedef struct AclspSpmmParams {
     uint32_t opB;            /* 0: B is k x n, 1: B is n x k and read transposed */
     uint32_t orderB;         /* 0 row-major, 1 column-major */
     uint32_t orderC;
-    uint32_t highPrecision;  /* 1: compensated fp32 accumulation (the FP32_HIGH_PRECISION algorithm) */
+    uint32_t highPrecision;  /* 1: the caller asked for FP32_HIGH_PRECISION; every algorithm sums in fp64, so unused */
     uint32_t reserved;
     int64_t ldb;
     int64_t ldc;

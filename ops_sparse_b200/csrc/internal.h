@@ -39,6 +39,16 @@ struct aclsparseContext {
     bool useUserWorkspace = false;
 };
 
+// A word of pinned host memory that a value from the device arrives in (host_flags.cpp).
+struct AclspHostSlot {
+    uint32_t* word = nullptr;
+    uint32_t index = 0;
+    uint64_t generation = 0;
+};
+AclspHostSlot AclspAcquireHostSlot();
+// True, and the value, once the device's copy has arrived and the slot still belongs to its holder.
+bool AclspHostSlotValue(const AclspHostSlot& slot, uint32_t* value);
+
 // What the most recent SpMV preprocessing of a matrix was built from.  The
 // buffer is reused by aclsparseSpMV only while every field still matches
 // (reference: sparse/spmv/arch35/spmv.h:47-107).
@@ -64,6 +74,9 @@ struct SpmvPlanRecord {
     int32_t alg = -1;
     const void* stream = nullptr;
     uint64_t streamEpoch = 0;
+    uint64_t serial = 0;          // AclspPublishPlan's answer for this build; 0: no plan
+    bool fromPreprocess = false;  // built by an explicit Preprocess call: only such a plan is reused
+    AclspHostSlot longestRow;     // where the plan's longest row arrives on the host
 };
 
 // SpMM preprocessing depends on the structure of A and on the width of C only.
@@ -81,6 +94,8 @@ struct SpmmPlanRecord {
     const void* stream = nullptr;
     uint64_t streamEpoch = 0;
     uint64_t ownerId = 0;
+    uint64_t serial = 0;
+    bool fromPreprocess = false;
 };
 
 struct aclsparseSpMatDescr {
@@ -141,6 +156,12 @@ struct aclsparseDnMatDescr {
 };
 
 uint64_t AclspNextWorkspaceOwnerId();
+
+// Plan ownership of workspace buffers (plan_registry.cpp).  AclspPublishPlan records that `buffer` now
+// holds a freshly built plan and returns its serial number; AclspPlanIsCurrent says whether the plan
+// with that serial is still the last one built in `buffer`.
+uint64_t AclspPublishPlan(const void* buffer);
+bool AclspPlanIsCurrent(const void* buffer, uint64_t serial);
 void AclspResetSpmvPlan(aclsparseSpMatDescr* descr);
 
 // Logging: ACLSPARSE_LOG_LEVEL=0 (off, default) / 1 (errors) / 2 (info) / 3 (debug) -> stderr.

@@ -26,12 +26,30 @@ __device__ __forceinline__ int ClampOffset(int v, int nnz)
     return v < 0 ? 0 : (v > nnz ? nnz : v);
 }
 
+// dst[i] = src[i * stride] - base for i in [0, rows]; with `longest` non-null also the longest row
+// (src[(i + 1) * stride] - src[i * stride], negative counted as 0), one atomicMax per warp.
 __global__ void NormalizeRowOffsetsKernel(const int32_t* __restrict__ src, int32_t* __restrict__ dst, uint32_t rows,
-                                          int32_t indexBase, int64_t stride)
+                                          int32_t indexBase, int64_t stride, uint32_t* __restrict__ longest)
 {
     const uint64_t step = static_cast<uint64_t>(gridDim.x) * blockDim.x;
+    int32_t best = 0;
     for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i <= rows; i += step) {
-        dst[i] = src[i * stride] - indexBase;
+        const int32_t here = src[i * stride];
+        dst[i] = here - indexBase;
+        if (longest != nullptr && i < rows) {
+            const int64_t len = static_cast<int64_t>(src[(i + 1) * stride]) - here;
+            const int32_t len32 = len > 0x7fffffff ? 0x7fffffff : static_cast<int32_t>(len);
+            best = len32 > best ? len32 : best;
+        }
+    }
+    if (longest != nullptr) {
+        for (int o = 16; o > 0; o >>= 1) {
+            const int32_t other = __shfl_xor_sync(0xffffffffu, best, o);
+            best = other > best ? other : best;
+        }
+        if ((threadIdx.x & 31) == 0 && best > 0) {
+            atomicMax(longest, static_cast<uint32_t>(best));
+        }
     }
 }
 
@@ -80,7 +98,6 @@ __global__ void TileSplitKernel(void* workspace, uint32_t rows, uint32_t cols, u
         h.carryOff = layout.carryOff;
         h.totalBytes = layout.totalBytes;
         *reinterpret_cast<AclspPlanHeader*>(base) = h;
-        *reinterpret_cast<uint32_t*>(base + ACLSP_HEADER_WAIT_FAILURES_OFF) = 0u;
     }
     if (t >= layout.numTiles) {
         return;
@@ -143,12 +160,18 @@ void AclspLaunchPlanBuild(const void* rowPtr, void* workspace, uint32_t rows, ui
     } else {
         aclspSpmvLayout(rows, nnz, &layout);
     }
-    auto* dst = reinterpret_cast<int32_t*>(static_cast<unsigned char*>(workspace) + layout.rowPtrOff);
+    auto* bytes = static_cast<unsigned char*>(workspace);
+    auto* dst = reinterpret_cast<int32_t*>(bytes + layout.rowPtrOff);
+    // The counters behind the header proper (bounded waits that ran out, longest row) start at zero.
+    cudaMemsetAsync(bytes + ACLSP_HEADER_WAIT_FAILURES_OFF, 0, ACLSP_HEADER_BYTES - ACLSP_HEADER_WAIT_FAILURES_OFF,
+                    stream);
+    auto* longest = kind == ACLSP_KIND_SPMV ? reinterpret_cast<uint32_t*>(bytes + ACLSP_HEADER_MAX_ROW_LEN_OFF)
+                                            : nullptr;
     const uint64_t entries = static_cast<uint64_t>(rows) + 1u;
     uint64_t blocks = (entries + 255u) / 256u;
     blocks = blocks > 148u * 16u ? 148u * 16u : blocks;
     NormalizeRowOffsetsKernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
-        static_cast<const int32_t*>(rowPtr), dst, rows, indexBase, rowOffsetsStride);
+        static_cast<const int32_t*>(rowPtr), dst, rows, indexBase, rowOffsetsStride, longest);
     const uint32_t splitBlocks = (layout.numTiles + 1u + 127u) / 128u;
     TileSplitKernel<<<splitBlocks, 128, 0, stream>>>(workspace, rows, cols, nnz, indexBase, tileItems, kind,
                                                      denseCols, classDiv, layout);

@@ -38,8 +38,13 @@
 #define ACLSP_KIND_SPMV 1u
 #define ACLSP_KIND_SPMM 2u
 /* Byte offset, inside the header, of a uint32 that counts the CTAs of the persistent SpMV kernel whose
- * bounded wait for a bulk copy ran out (0 after every healthy product; zeroed by the preprocessing pass). */
+ * bounded wait for a bulk copy ran out (0 after every healthy product; zeroed by the preprocessing pass).
+ * Such a warp finishes its rows with plain loads, so the count is a diagnosis, not an error. */
 #define ACLSP_HEADER_WAIT_FAILURES_OFF 128u
+/* Byte offset, inside the header, of a uint32 with the longest row of the matrix (row offsets taken as
+ * they are: a negative length counts as 0), written by the SpMV preprocessing pass.  The SpMV kernels
+ * choose between row blocks and merge-path tiles by it. */
+#define ACLSP_HEADER_MAX_ROW_LEN_OFF 132u
 
 /* Merge items per tile. */
 #define ACLSP_SPMV_TILE_ITEMS 2048u

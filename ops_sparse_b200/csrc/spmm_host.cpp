@@ -14,10 +14,11 @@
  *    the structure of A and the width of C only: calling with another B, C,
  *    alpha or beta reuses it (the reference rebuilds, spmm_host.cpp:63-97,199-215);
  *  - every algorithm value selects the same kernels, which add in a fixed
- *    order (so all of them are deterministic, as the reference's CSR_ALG3 is);
- *    FP32_HIGH_PRECISION additionally compensates the fp32 accumulation (the
- *    reference's variant is Kahan, spmm_kernel_simt.cpp:424-431; this one is Dot2:
- *    error-free products and error-free sums, which also holds in cancelling rows).
+ *    order (so all of them are deterministic, as the reference's CSR_ALG3 is) and
+ *    with fp64 products and fp64 row sums (so all of them are at least as
+ *    accurate as the reference's FP32_HIGH_PRECISION, which is Kahan-compensated
+ *    fp32, spmm_kernel_simt.cpp:424-431, and equal its fp64 test golden up to
+ *    the order of the additions, also in cancelling rows and on Inf / NaN data).
  */
 #include <cstdint>
 #include <limits>
@@ -159,12 +160,16 @@ aclsparseStatus_t CheckBuffer(const void* buffer)
 bool PlanMatches(const aclsparseSpMatDescr* a, uint64_t denseCols, const void* buffer, const aclsparseContext* h)
 {
     const SpmmPlanRecord& p = a->spmm;
-    return a->activeBuffer == buffer && p.buffer == buffer && p.rowOffsets == a->ptrs && p.rows == a->rows &&
+    // Only a plan from an explicit Preprocess call is reused, and only while no later plan build (of this
+    // or any other descriptor, SpMM or SpMV) went into the same buffer.
+    return a->activeBuffer == buffer && p.buffer == buffer && p.fromPreprocess && AclspPlanIsCurrent(buffer, p.serial) &&
+           p.rowOffsets == a->ptrs && p.rows == a->rows &&
            p.cols == a->cols && p.nnz == a->nnz && p.denseCols == denseCols && p.base == a->baseType &&
            p.stream == h->stream && p.streamEpoch == h->streamEpoch && p.ownerId == a->workspaceOwnerId;
 }
 
-aclsparseStatus_t BuildPlan(aclsparseContext* h, aclsparseSpMatDescr* a, uint64_t denseCols, void* buffer)
+aclsparseStatus_t BuildPlan(aclsparseContext* h, aclsparseSpMatDescr* a, uint64_t denseCols, void* buffer,
+                            bool fromPreprocess)
 {
     (void)cudaGetLastError();
     spmm_b200_preprocess_kernel_do(a->ptrs, buffer, static_cast<uint32_t>(a->rows), static_cast<uint32_t>(a->cols),
@@ -176,6 +181,8 @@ aclsparseStatus_t BuildPlan(aclsparseContext* h, aclsparseSpMatDescr* a, uint64_
         return ACL_SPARSE_STATUS_EXECUTION_FAILED;
     }
     SpmmPlanRecord& p = a->spmm;
+    p.serial = AclspPublishPlan(buffer);
+    p.fromPreprocess = fromPreprocess;
     p.buffer = buffer;
     p.rowOffsets = a->ptrs;
     p.rows = a->rows;
@@ -242,7 +249,7 @@ extern "C" aclsparseStatus_t aclsparseSpMMPreprocess(aclsparseHandle_t handle, a
     if (st != ACL_SPARSE_STATUS_SUCCESS) {
         return st;
     }
-    return BuildPlan(handle, const_cast<aclsparseSpMatDescr*>(matA), static_cast<uint64_t>(matC->cols), buffer);
+    return BuildPlan(handle, const_cast<aclsparseSpMatDescr*>(matA), static_cast<uint64_t>(matC->cols), buffer, true);
 }
 
 extern "C" aclsparseStatus_t aclsparseSpMM(aclsparseHandle_t handle, aclsparseOperation_t opA,
@@ -268,7 +275,7 @@ extern "C" aclsparseStatus_t aclsparseSpMM(aclsparseHandle_t handle, aclsparseOp
     // Preprocess is optional: without a matching plan in this buffer it is
     // built here, on the same stream, ahead of the product.
     if (!PlanMatches(a, n, buffer, handle)) {
-        st = BuildPlan(handle, a, n, buffer);
+        st = BuildPlan(handle, a, n, buffer, false);
         if (st != ACL_SPARSE_STATUS_SUCCESS) {
             return st;
         }

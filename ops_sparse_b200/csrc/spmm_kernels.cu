@@ -24,6 +24,12 @@
  *      neighbours go to the plan's carry area and are combined in tile order
  *      by a second kernel.  All orders are fixed: results are reproducible.
  *
+ * Accuracy.  Products and row sums are fp64 (exact products of fp32 factors,
+ * which cannot overflow), alpha * sum + beta * C is evaluated in fp64 and
+ * rounded once: a row equals the reference's fp64 test golden (SpmmGolden,
+ * test/spmm_op/spmm_op_golden.h:142-205) up to the order of the additions,
+ * whatever the data, for every algorithm value.
+ *
  * Layouts.  VW in {4, 2, 1} floats per lane is the widest vector the operands
  * allow (unit column stride of op(B) and C, leading dimensions and base
  * addresses aligned to the vector).  VW = 1 addresses both matrices through
@@ -174,7 +180,7 @@ constexpr size_t SmemBytes(int vw)
            + sizeof(int) * (2 * kWarps + 2);            // warp row split, head flags
 }
 
-template <int VW, bool kCompensated, bool kStageB>
+template <int VW, bool kStageB>
 __global__ void __launch_bounds__(kThreads)
 SpmmTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ values, const float* __restrict__ B,
                float* __restrict__ C, SpmmPlanView plan, AclspSpmmParams p, DenseStrides ds)
@@ -286,15 +292,15 @@ SpmmTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ val
         const float* bLane = B + static_cast<int64_t>(colL) * ds.bCol;
         float* cLane = C + static_cast<int64_t>(colL) * ds.cCol;
 
-        // acc is the running fp32 sum; with kCompensated, comp collects the rounding
-        // errors of every addition and every product, so that acc + comp carries
-        // the row sum to roughly twice fp32 precision.
-        float acc[VW];
-        float comp[VW];
+        // The running sum of the row piece: an fp64 sum of fp64 products.  Products of fp32 factors are
+        // exact in fp64 and cannot overflow, so a row equals the fp64 golden (SpmmGolden,
+        // test/spmm_op/spmm_op_golden.h:142-205) up to the order of the additions, Inf and NaN included,
+        // whatever the data.  Measured against fp32 FMA row sums on the gather-bound benchmark
+        // configurations: 8 to 15 % more kernel time; fp32 sums miss the 1e-5 / 1e-6 tolerance on cancelling rows.
+        double acc[VW];
 #pragma unroll
         for (int v = 0; v < VW; ++v) {
-            acc[v] = 0.0f;
-            comp[v] = 0.0f;
+            acc[v] = 0.0;
         }
         auto issue = [&](int q) {
             const int c = sCol[q];
@@ -302,10 +308,6 @@ SpmmTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ val
                 CpAsync<4 * VW>(ring + (q % kStages) * kPanel, bLane + static_cast<int64_t>(c) * ds.bRow);
             }
             CpAsyncCommit();
-        };
-        auto value = [&](int v) -> double {
-            return kCompensated ? static_cast<double>(acc[v]) + static_cast<double>(comp[v])
-                                : static_cast<double>(acc[v]);
         };
         // C[row] = alpha * sum + beta * C[row]; beta == 0 never reads C.
         auto storeRow = [&](int localRow, const double (&sum)[VW]) {
@@ -322,13 +324,8 @@ SpmmTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ val
             float* o = reinterpret_cast<float*>(&out);
 #pragma unroll
             for (int v = 0; v < VW; ++v) {
-                if (kCompensated) {
-                    const double r = static_cast<double>(sc.alpha) * sum[v];
-                    o[v] = static_cast<float>(sc.betaZero ? r : r + static_cast<double>(sc.beta) * od[v]);
-                } else {
-                    const float f = static_cast<float>(sum[v]);
-                    o[v] = sc.betaZero ? sc.alpha * f : sc.alpha * f + sc.beta * od[v];
-                }
+                const double r = static_cast<double>(sc.alpha) * sum[v];
+                o[v] = static_cast<float>(sc.betaZero ? r : r + static_cast<double>(sc.beta) * od[v]);
             }
             *reinterpret_cast<V*>(dst) = out;
             // Mirrors of C (the other GPUs' result buffers when the matrix is
@@ -348,7 +345,7 @@ SpmmTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ val
             double sum[VW];
 #pragma unroll
             for (int v = 0; v < VW; ++v) {
-                sum[v] = value(v);
+                sum[v] = acc[v];
             }
             if (first && headOpen) {
                 if (colOk) {
@@ -363,8 +360,7 @@ SpmmTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ val
             first = false;
 #pragma unroll
             for (int v = 0; v < VW; ++v) {
-                acc[v] = 0.0f;
-                comp[v] = 0.0f;
+                acc[v] = 0.0;
             }
         };
 
@@ -374,21 +370,7 @@ SpmmTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ val
             const float* bv = reinterpret_cast<const float*>(&b);
 #pragma unroll
             for (int v = 0; v < VW; ++v) {
-                if (kCompensated) {
-                    // Dot2 (Ogita, Rump, Oishi): error-free product and error-free sum,
-                    // both errors collected in comp; acc + comp is the dot product as if
-                    // accumulated in twice the working precision.  TwoSum, unlike Kahan's
-                    // shortcut, is exact whatever the magnitudes, i.e. also while a row cancels.
-                    const float prod = __fmul_rn(a, bv[v]);
-                    const float perr = fmaf(a, bv[v], -prod);  // a*b == prod + perr
-                    const float tsum = __fadd_rn(acc[v], prod);
-                    const float bp = __fsub_rn(tsum, acc[v]);
-                    const float serr = __fadd_rn(__fsub_rn(acc[v], __fsub_rn(tsum, bp)), __fsub_rn(prod, bp));
-                    comp[v] = __fadd_rn(comp[v], __fadd_rn(serr, perr));
-                    acc[v] = tsum;
-                } else {
-                    acc[v] = fmaf(a, bv[v], acc[v]);
-                }
+                acc[v] = fma(static_cast<double>(a), static_cast<double>(bv[v]), acc[v]);
             }
         };
         if (kStageB) {
@@ -460,7 +442,7 @@ SpmmTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ val
         if (colOk) {  // what is left belongs to the row that continues past this warp
 #pragma unroll
             for (int v = 0; v < VW; ++v) {
-                sTail[warp * kPanel + lane * VW + v] = value(v);
+                sTail[warp * kPanel + lane * VW + v] = acc[v];
             }
         }
         CpAsyncWait<0>();
@@ -558,16 +540,16 @@ __global__ void SpmmCarryFixupKernel(float* __restrict__ C, SpmmPlanView plan, A
     }
 }
 
-template <int VW, bool kCompensated, bool kStageB>
+template <int VW, bool kStageB>
 void Launch(const void* colInd, const void* values, const void* b, void* c, const SpmmPlanView& plan,
             const AclspSpmmParams& p, const DenseStrides& ds, cudaStream_t s)
 {
     constexpr size_t smem = SmemBytes(VW);
     // More than 48 KiB of dynamic shared memory has to be requested per kernel
     // and per device; the attribute is cheap to set, so it is set every time.
-    cudaFuncSetAttribute(SpmmTileKernel<VW, kCompensated, kStageB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaFuncSetAttribute(SpmmTileKernel<VW, kStageB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                          static_cast<int>(smem));
-    SpmmTileKernel<VW, kCompensated, kStageB><<<plan.numTiles, kThreads, smem, s>>>(
+    SpmmTileKernel<VW, kStageB><<<plan.numTiles, kThreads, smem, s>>>(
         static_cast<const int32_t*>(colInd), static_cast<const float*>(values), static_cast<const float*>(b),
         static_cast<float*>(c), plan, p, ds);
 }
@@ -583,16 +565,10 @@ void LaunchByPrecision(const void* colInd, const void* values, const void* b, vo
         const char* e = std::getenv("ACLSPARSE_SPMM_STAGE_B");
         return e == nullptr || e[0] != '0';
     }();
-    if (p.highPrecision != 0) {
-        if (stage) {
-            Launch<VW, true, true>(colInd, values, b, c, plan, p, ds, s);
-        } else {
-            Launch<VW, true, false>(colInd, values, b, c, plan, p, ds, s);
-        }
-    } else if (stage) {
-        Launch<VW, false, true>(colInd, values, b, c, plan, p, ds, s);
+    if (stage) {
+        Launch<VW, true>(colInd, values, b, c, plan, p, ds, s);
     } else {
-        Launch<VW, false, false>(colInd, values, b, c, plan, p, ds, s);
+        Launch<VW, false>(colInd, values, b, c, plan, p, ds, s);
     }
 }
 

@@ -243,8 +243,11 @@ bool PlanMatches(const aclsparseSpMatDescr* mat, const aclsparseDnVecDescr* x, c
                  aclsparseOperation_t opA, aclDataType computeType, aclsparseSpMVAlg_t alg, const void* buffer,
                  const aclsparseContext* h)
 {
+    // Only a plan from an explicit Preprocess call is reused, and only while no later plan build (of this
+    // or any other descriptor, SpMV or SpMM) went into the same buffer.
     const SpmvPlanRecord& p = mat->spmv;
-    return buffer != nullptr && p.buffer == buffer && mat->activeBuffer != buffer && p.rowOffsets == mat->ptrs &&
+    return buffer != nullptr && p.buffer == buffer && p.fromPreprocess && AclspPlanIsCurrent(buffer, p.serial) &&
+           mat->activeBuffer != buffer && p.rowOffsets == mat->ptrs &&
            p.colIndices == mat->idxs && p.values == mat->values && p.rowOffsetsStride == mat->ptrStride &&
            p.colIndStride == mat->idxStride && p.valuesStride == mat->valueStride && p.xStride == x->stride &&
            p.yStride == y->stride && p.rows == mat->rows && p.cols == mat->cols && p.nnz == mat->nnz &&
@@ -255,9 +258,11 @@ bool PlanMatches(const aclsparseSpMatDescr* mat, const aclsparseDnVecDescr* x, c
 
 void RecordPlan(aclsparseSpMatDescr* mat, const aclsparseDnVecDescr* x, const aclsparseDnVecDescr* y,
                 aclsparseOperation_t opA, aclDataType computeType, aclsparseSpMVAlg_t alg, const void* buffer,
-                const aclsparseContext* h)
+                const aclsparseContext* h, bool fromPreprocess)
 {
     SpmvPlanRecord& p = mat->spmv;
+    p.serial = AclspPublishPlan(buffer);
+    p.fromPreprocess = fromPreprocess;
     p.buffer = buffer;
     p.rowOffsets = mat->ptrs;
     p.colIndices = mat->idxs;
@@ -283,12 +288,20 @@ void RecordPlan(aclsparseSpMatDescr* mat, const aclsparseDnVecDescr* x, const ac
 
 // Enqueues the plan-building kernels.  An enqueue failure is attributed to
 // this launch only: the sticky-free last error is cleared first, then peeked.
-aclsparseStatus_t LaunchPreprocess(const aclsparseContext* h, const aclsparseSpMatDescr* mat, void* buffer)
+aclsparseStatus_t LaunchPreprocess(const aclsparseContext* h, aclsparseSpMatDescr* mat, void* buffer)
 {
     (void)cudaGetLastError();
     spmv_b200_preprocess_kernel_do(mat->ptrs, buffer, static_cast<uint32_t>(mat->rows),
                                    static_cast<uint32_t>(mat->cols), static_cast<uint32_t>(mat->nnz),
                                    static_cast<int32_t>(mat->baseType), mat->ptrStride, h->stream);
+    // The longest row, which the pass has just written into the plan header, is sent to pinned host
+    // memory in stream order; products look there to pick their kernel and never wait for it.
+    mat->spmv.longestRow = AclspAcquireHostSlot();
+    if (mat->spmv.longestRow.word != nullptr) {
+        (void)cudaMemcpyAsync(mat->spmv.longestRow.word,
+                              static_cast<const unsigned char*>(buffer) + ACLSP_HEADER_MAX_ROW_LEN_OFF, sizeof(uint32_t),
+                              cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(h->stream));
+    }
     const cudaError_t err = cudaPeekAtLastError();
     if (err != cudaSuccess) {
         ACLSP_LOGE(kApi, "preprocess enqueue failed: %s", cudaGetErrorString(err));
@@ -349,7 +362,7 @@ extern "C" aclsparseStatus_t aclsparseSpMVPreprocess(aclsparseHandle_t handle, a
             return st;
         }
     }
-    RecordPlan(mat, vecX, vecY, opA, computeType, alg, externalBuffer, handle);
+    RecordPlan(mat, vecX, vecY, opA, computeType, alg, externalBuffer, handle, true);
     return ACL_SPARSE_STATUS_SUCCESS;
 }
 
@@ -374,10 +387,10 @@ extern "C" aclsparseStatus_t aclsparseSpMV(aclsparseHandle_t handle, aclsparseOp
     if (mat->rows == 0) {  // nothing to write
         return ACL_SPARSE_STATUS_SUCCESS;
     }
-    // Preprocess is optional.  Without a matching plan in this buffer the plan
-    // is (re)built here, on the same stream and ahead of the product, so that
-    // a caller who never preprocesses, or who let another operator overwrite
-    // the buffer, still gets the product of the descriptor's current arrays.
+    // Preprocess is optional.  Without a matching plan from a Preprocess call in this buffer the
+    // plan is (re)built here, on the same stream and ahead of the product (a few O(rows) kernels),
+    // so that a caller who never preprocesses, or who let another operator or another matrix
+    // overwrite the buffer, still gets the product of the descriptor's current arrays.
     if (!PlanMatches(mat, vecX, vecY, opA, computeType, alg, externalBuffer, handle)) {
         if (mat->activeBuffer == externalBuffer) {
             mat->activeBuffer = nullptr;
@@ -386,7 +399,7 @@ extern "C" aclsparseStatus_t aclsparseSpMV(aclsparseHandle_t handle, aclsparseOp
         if (st != ACL_SPARSE_STATUS_SUCCESS) {
             return st;
         }
-        RecordPlan(mat, vecX, vecY, opA, computeType, alg, externalBuffer, handle);
+        RecordPlan(mat, vecX, vecY, opA, computeType, alg, externalBuffer, handle, false);
     }
 
     AclspSpmvParams params{};
@@ -405,6 +418,11 @@ extern "C" aclsparseStatus_t aclsparseSpMV(aclsparseHandle_t handle, aclsparseOp
     } else {
         params.alpha = *static_cast<const float*>(alpha);
         params.beta = *static_cast<const float*>(beta);
+    }
+    params.maxRowLenHint = ACLSP_MAX_ROW_LEN_UNKNOWN;
+    uint32_t longest = 0;
+    if (AclspHostSlotValue(mat->spmv.longestRow, &longest)) {
+        params.maxRowLenHint = longest;
     }
     params.numMirrors = static_cast<uint32_t>(vecY->numMirrors);
     params.mirrorMulticast = vecY->mirrorMulticast ? 1u : 0u;

@@ -1,11 +1,34 @@
 /*
  * CSR SpMV for sm_100a:  y = alpha * A * x + beta * y,  fp32 data, int32 indices.
  *
- * Work decomposition.  The matrix is cut along the merge path of (row ends,
- * non-zeros) into tiles of kTile items, so a tile holds at most kTile
- * non-zeros plus rows whatever the row-length distribution: short rows, empty
- * rows and 200 000-entry rows all cost the same per item.  One CTA owns one
- * tile:
+ * Two kernels.  The preprocessing pass records the longest row of the matrix in
+ * the plan header and sends a copy to pinned host memory, asynchronously.  Once
+ * that copy has arrived the host launches the kernel that fits; until then (the
+ * first product right after a Preprocess call) it launches both, and each looks
+ * in the plan header to see whether the product is its to compute.
+ *
+ * A. Row blocks (SpmvRowBlockKernel), for matrices whose longest row is short
+ *    (a stencil, a mesh, a k-regular graph).  A block is 32 consecutive rows;
+ *    its non-zeros are one contiguous slice of colInd / values.  Persistent
+ *    warps loop over blocks.  No thread issues a global load for the matrix:
+ *    lane 0 asks the copy engine (cp.async.bulk, completion counted on an
+ *    mbarrier) for the slices and the 33 row offsets of the block kStages
+ *    turns ahead, into the warp's own shared-memory stages, so HBM streams
+ *    for some warps while the others compute (a stage is sized for the longest
+ *    row, so that as many warps as possible are resident: measured on the
+ *    27-point stencil, 24 warps with one stage each beat 12 warps with two).
+ *    Each lane then walks ONE row out of
+ *    shared memory with sixteen gathers of x in flight, adds in registers and
+ *    writes y: no shuffle, no barrier, no carry.  The lanes of a warp are on
+ *    consecutive rows at the same position, so for banded matrices their
+ *    gathers fall into one or two lines of x.  Every wait is bounded; a warp
+ *    whose wait runs out stops using the copy engine and finishes its blocks
+ *    with plain loads, so the product is still right.
+ *
+ * B. Merge-path tiles (SpmvTileKernel), for everything else.  The matrix is cut
+ *    along the merge path of (row ends, non-zeros) into tiles of kTile items, so
+ *    a tile holds at most kTile non-zeros plus rows whatever the row-length
+ *    distribution.  One CTA owns one tile:
  *   1. the tile's slice of colInd / values is streamed with 128-bit loads
  *      (evict-first: it is read exactly once), x[col] is gathered through the
  *      read-only path, and every product is staged in shared memory as an
@@ -23,12 +46,18 @@
  *      in tile order and writes that row.
  * Every sum is taken in a fixed order, so results are bit-reproducible.
  *
- * Accuracy.  Every product is kept exactly (hi + lo) and the hi parts are summed
- * in fp64 (the lo parts, 2^-24 of the products, in fp32), so
- * a row is as accurate as the reference's host golden (SpmvCpu with a double
- * accumulator, test/spmv/arch22/spmv_test.cpp:258-279,309-348) up to the order
- * of the additions; the reference's device kernels reach for compensated
- * arithmetic for the same reason (sparse/spmv/arch22/kernels/spmv_kernel.h:19-68).
+ * Accuracy.  Every product is kept exactly (hi + lo, rounded product and its
+ * rounding error by FMA); the hi parts are summed in fp64, the lo parts (2^-24
+ * of the products) in fp32, alpha * sum + beta * y is evaluated in fp64 and
+ * rounded once, so a row is as accurate as the reference's host golden (SpmvCpu
+ * with a double accumulator, test/spmv/arch22/spmv_test.cpp:258-279,309-348) up
+ * to the order of the additions; the reference's device kernels reach for
+ * compensated arithmetic for the same reason
+ * (sparse/spmv/arch22/kernels/spmv_kernel.h:19-68).  A row piece whose sum is
+ * not finite (an fp32 product overflowed, or the data holds Inf / NaN) is
+ * summed again with fp64 products, which cannot overflow, so it again equals
+ * the golden; the reference's device code falls back to its uncompensated sum
+ * there (sparse/spmv/arch35/spmv_kernel.cpp:459-484).
  *
  * The kernels never read or write out of bounds for any content of the index
  * arrays: offsets are clamped to [0, nnz] and entries whose column falls
@@ -157,6 +186,27 @@ __device__ __forceinline__ void Product(float a, int32_t rawCol, const float* __
     lo = fmaf(a, xv, -hi);
 }
 
+__device__ __forceinline__ bool Finite(double v)
+{
+    return fabs(v) <= 1.7976931348623157e308;
+}
+
+// Non-zeros [e0, e1) of the arrays multiplied and added in fp64, in array order.  Rare (only
+// for sums that came out non-finite), so it is kept out of line and takes everything by value.
+__device__ __forceinline__ double ExactSum(const int32_t* colInd, const float* values, const float* x, int64_t e0,
+                                        int64_t e1, int64_t colIndStride, int64_t valuesStride, int64_t xStride,
+                                        uint32_t indexBase, uint32_t cols)
+{
+    double s = 0.0;
+    for (int64_t e = e0; e < e1; ++e) {
+        const uint32_t col = static_cast<uint32_t>(colInd[e * colIndStride]) - indexBase;
+        if (col < cols) {
+            s += static_cast<double>(values[e * valuesStride]) * static_cast<double>(x[static_cast<int64_t>(col) * xStride]);
+        }
+    }
+    return s;
+}
+
 /* ------------------------------------------------------------- reduce -- */
 
 // Shared scratch of the reduction, one per CTA.
@@ -171,6 +221,10 @@ struct ReduceScratch {
 // The staged tile: nt exact products (hi, lo), the nr + 1 row offsets relative
 // to the tile's first product, and nr spare words for the mirrors of y.
 struct StagedTile {
+    const int32_t* colInd;  // the global arrays, for the exact recomputation of a non-finite piece
+    const float* values;
+    const float* x;
+    int j0;                 // index of the tile's first product in them
     int t;
     int i0;
     int i1;
@@ -220,6 +274,11 @@ __device__ __forceinline__ void ReduceTile(const StagedTile& st, float* __restri
         return e < 0 ? 0 : (e > nt ? nt : e);
     };
     auto emit = [&](int k, double sum) {
+        if (!Finite(sum)) {
+            sum = ExactSum(st.colInd, st.values, st.x, static_cast<int64_t>(st.j0) + segBegin(k),
+                           static_cast<int64_t>(st.j0) + segEnd(k), p.colIndStride, p.valuesStride, p.xStride,
+                           p.indexBase, p.cols);
+        }
         if (k >= nr) {
             plan.carry[2 * t] = sum;
         } else if (k == 0 && headOpen) {
@@ -379,10 +438,14 @@ __device__ __forceinline__ void ReduceTile(const StagedTile& st, float* __restri
 /* --------------------------------------------- one CTA per tile -- */
 
 template <bool kVector>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, kVector ? 6 : 1)
 SpmvTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ values, const float* __restrict__ x,
-               float* __restrict__ y, SpmvPlanView plan, AclspSpmvParams p)
+               float* __restrict__ y, SpmvPlanView plan, AclspSpmvParams p, const uint32_t* __restrict__ maxRowLen,
+               uint32_t rowBlockCap)
 {
+    if (rowBlockCap != 0 && *maxRowLen <= rowBlockCap) {
+        return;  // every row is short: the row-block kernel computes this product
+    }
     // One pool of 32-bit words: the hi parts of the tile's products, their lo
     // parts, and the tile's row offsets packed against the end.  A tile has nt
     // products and nr + 1 offsets with nt + nr <= kTile.
@@ -497,6 +560,10 @@ SpmvTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ val
     __syncthreads();
 
     StagedTile st;
+    st.colInd = colInd;
+    st.values = values;
+    st.x = x;
+    st.j0 = j0;
     st.t = t;
     st.i0 = i0;
     st.i1 = i1;
@@ -510,60 +577,18 @@ SpmvTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ val
     ReduceTile(st, y, plan, p, scratch);
 }
 
-/* ------------------------------------- persistent, bulk-copy fed -- */
+/* ------------------------------------------------ row blocks (A) -- */
 
-// The same tile work inside a persistent CTA that never issues a global load
-// for the matrix: thread 0 asks the copy engine (cp.async.bulk, completion on an
-// mbarrier) for the tile's slice of values, colInd and row offsets kStreamStages
-// tiles ahead, straight into the shared-memory words where the products will
-// replace them.  Measured on B200 (27-point stencil, 4.1 M rows): the copies
-// alone stream at 6.7 TB/s, but a CTA needs about 3.6 us of dependent latency per
-// tile (x gather, barriers, reduction) whatever runs beside it, and the stages
-// leave room for only 4 CTAs per SM, so the whole product takes 0.33 ms against
-// 0.26 ms for the one-CTA-per-tile kernel with its 6 CTAs per SM.  It is
-// therefore opt-in (ACLSPARSE_SPMV_STREAM=1) and kept bit-identical to the
-// default kernel by the tests.
-constexpr int kStreamStages = 3;
-constexpr int kStageWords = 2 * kTile + 24;
-constexpr int kStreamCtasPerSm = 4;
+constexpr int kBlockRows = 32;             // rows per block: one per lane
+constexpr int kOffsetWords = 36;           // 33 row offsets, rounded up to whole 16-byte vectors
 constexpr uint32_t kSpinLimit = 1u << 18;  // polls of about a microsecond before a wait is given up
 
-struct TileGeom {
-    int i0, i1, j0, nr, nt;
-    int a0, shift, span;     // first 4-aligned array index, distance of the tile's first product from it, words staged
-    int copyElems;           // leading part of the span that is whole vectors inside the arrays: bulk-copied
-    int offFirst, offShift;  // first 4-aligned row offset copied, distance of row i0 from it
-    int offWords;
-    bool valid;
-};
-
-__device__ __forceinline__ TileGeom Geometry(uint32_t t, int i0, int i1, const AclspSpmvParams& p)
-{
-    TileGeom g;
-    const int nnz = static_cast<int>(p.nnz);
-    const int64_t total = static_cast<int64_t>(p.rows) + nnz;
-    int64_t d0 = static_cast<int64_t>(t) * kTile;
-    int64_t d1 = d0 + kTile;
-    d0 = d0 < total ? d0 : total;
-    d1 = d1 < total ? d1 : total;
-    g.i0 = i0;
-    g.i1 = i1;
-    g.j0 = static_cast<int>(d0 - i0);
-    const int j1 = static_cast<int>(d1 - i1);
-    g.nr = i1 - i0;
-    g.nt = j1 - g.j0;
-    g.valid = !(g.nr < 0 || g.nt < 0 || g.nr + g.nt > kTile || i0 < 0 || i1 > static_cast<int>(p.rows) || g.j0 < 0 ||
-                j1 > nnz);
-    g.a0 = g.j0 & ~3;
-    g.shift = g.j0 - g.a0;
-    g.span = (g.nt + g.shift + 3) & ~3;
-    const int whole = (nnz & ~3) - g.a0;
-    g.copyElems = whole < 0 ? 0 : (whole < g.span ? whole : g.span);
-    g.offFirst = i0 & ~3;
-    g.offShift = i0 - g.offFirst;
-    g.offWords = (g.nr + 1 + g.offShift + 3) & ~3;
-    return g;
-}
+// Words of one stage for rows of at most `cap` non-zeros: the offsets, then the slice of
+// values and the slice of colInd, each from the 4-aligned array index below the block's first
+// non-zero to the 4-aligned index above its last.
+__host__ __device__ constexpr int RowBlockSpanCap(int cap) { return kBlockRows * cap + 8; }
+__host__ __device__ constexpr int RowBlockStageWords(int cap) { return kOffsetWords + 2 * RowBlockSpanCap(cap); }
+constexpr int kRowBlockMaxLen = 40;  // longest row the row-block kernel is used for
 
 __device__ __forceinline__ uint32_t SharedAddress(const void* ptr)
 {
@@ -571,7 +596,7 @@ __device__ __forceinline__ uint32_t SharedAddress(const void* ptr)
 }
 
 // The matrix is read once per product: its lines are marked evict-first in L2 so
-// that they do not push x (which every tile gathers from) out of it.
+// that they do not push x (which every block gathers from) out of it.
 __device__ __forceinline__ uint64_t EvictFirstPolicy()
 {
     uint64_t policy;
@@ -579,6 +604,7 @@ __device__ __forceinline__ uint64_t EvictFirstPolicy()
     return policy;
 }
 
+// Bulk copy into this CTA's shared memory; the source is this GPU's own memory; no multicast.
 __device__ __forceinline__ void BulkLoad(void* smemDst, const void* gmemSrc, uint32_t bytes, uint64_t* bar,
                                          uint64_t policy)
 {
@@ -587,24 +613,6 @@ __device__ __forceinline__ void BulkLoad(void* smemDst, const void* gmemSrc, uin
             "r"(SharedAddress(smemDst)),
         "l"(gmemSrc), "r"(bytes), "r"(SharedAddress(bar)), "l"(policy)
         : "memory");
-}
-
-// Thread 0: announce the bytes of a tile to the stage's barrier and start its copies.
-__device__ __forceinline__ void IssueTile(const TileGeom& g, float* stage, uint64_t* bar, const int32_t* colInd,
-                                          const float* values, const int32_t* rowPtr, uint64_t policy)
-{
-    const uint32_t arrayBytes = g.valid ? 4u * static_cast<uint32_t>(g.copyElems) : 0u;
-    const uint32_t offBytes = g.valid ? 4u * static_cast<uint32_t>(g.offWords) : 0u;
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(SharedAddress(bar)),
-                 "r"(2u * arrayBytes + offBytes)
-                 : "memory");
-    if (arrayBytes != 0) {
-        BulkLoad(stage, values + g.a0, arrayBytes, bar, policy);
-        BulkLoad(stage + g.span, colInd + g.a0, arrayBytes, bar, policy);
-    }
-    if (offBytes != 0) {
-        BulkLoad(stage + 2 * g.span, rowPtr + g.offFirst, offBytes, bar, policy);
-    }
 }
 
 // Bounded wait for a stage: false when the copies have not landed after kSpinLimit polls.
@@ -629,204 +637,334 @@ __device__ __forceinline__ bool WaitStage(uint64_t* bar, uint32_t parity)
     return false;
 }
 
-template <int kStages, int kCtas>
-__global__ void __launch_bounds__(kThreads, kCtas)
-SpmvStreamKernel(const int32_t* __restrict__ colInd, const float* __restrict__ values, const float* __restrict__ x,
-                 float* __restrict__ y, SpmvPlanView plan, AclspSpmvParams p, uint32_t* __restrict__ waitFailures)
+struct RowBlockGeom {
+    int r0;         // first row
+    int nrows;      // rows in the block (32 except at the end of the matrix)
+    int a0;         // 4-aligned array index the staged slices start at
+    int span;       // words staged per slice
+    int copyElems;  // leading part of the span that is whole vectors inside the arrays: bulk-copied
+    int offWords;   // row offsets copied, whole vectors
+    bool valid;     // false: offsets inconsistent with the recorded longest row; nothing is copied
+};
+
+// j0 / j1: offsets of the block's first row and of the row after its last one, as loaded from the plan.
+__device__ __forceinline__ RowBlockGeom BlockGeometry(uint32_t block, int j0, int j1, const AclspSpmvParams& p,
+                                                      int spanCap)
 {
-    extern __shared__ __align__(128) unsigned char smemRaw[];
-    float* stages = reinterpret_cast<float*>(smemRaw);                                   // kStages * kStageWords
-    uint64_t* full = reinterpret_cast<uint64_t*>(stages + kStages * kStageWords);  // kStages barriers
-    ReduceScratch& scratch = *reinterpret_cast<ReduceScratch*>(full + kStages);
-
-    const int tid = threadIdx.x;
+    RowBlockGeom g;
     const int nnz = static_cast<int>(p.nnz);
-    const uint32_t numTiles = plan.numTiles;
-    const uint32_t stride = gridDim.x;
-    const uint64_t policy = EvictFirstPolicy();
+    g.r0 = static_cast<int>(block) * kBlockRows;
+    const int left = static_cast<int>(p.rows) - g.r0;
+    g.nrows = left < kBlockRows ? left : kBlockRows;
+    j0 = ClampOffset(j0, nnz);
+    j1 = ClampOffset(j1, nnz);
+    g.a0 = j0 & ~3;
+    g.span = (j1 - g.a0 + 3) & ~3;
+    g.valid = j1 >= j0 && g.span <= spanCap;
+    const int whole = (nnz & ~3) - g.a0;
+    g.copyElems = whole < 0 ? 0 : (whole < g.span ? whole : g.span);
+    g.offWords = (g.nrows + 1 + 3) & ~3;
+    return g;
+}
 
-    if (tid == 0) {
-        for (int sIdx = 0; sIdx < kStages; ++sIdx) {
-            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(SharedAddress(full + sIdx)) : "memory");
-        }
-        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
-        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-        uint32_t t = blockIdx.x;
-        for (int sIdx = 0; sIdx < kStages && t < numTiles; ++sIdx, t += stride) {
-            const TileGeom g = Geometry(t, plan.tileRow[t], plan.tileRow[t + 1], p);
-            IssueTile(g, stages + sIdx * kStageWords, full + sIdx, colInd, values, plan.rowPtr, policy);
-        }
-    }
-    __syncthreads();
-
-    // Split points and row bin of the tile after this one, fetched a tile ahead.
-    uint32_t t = blockIdx.x;
-    int nextI0 = 0, nextI1 = 0, nextCls = 0;
-    if (t < numTiles) {
-        nextI0 = plan.tileRow[t];
-        nextI1 = plan.tileRow[t + 1];
-        nextCls = plan.tileClass[t];
-    }
-    bool waitedOut = false;
-    for (uint32_t it = 0; t < numTiles; ++it, t += stride) {
-        const int sIdx = static_cast<int>(it % kStages);
-        const uint32_t parity = (it / kStages) & 1u;
-        float* stage = stages + sIdx * kStageWords;
-        const TileGeom g = Geometry(t, nextI0, nextI1, p);
-        const int cls = nextCls;
-        const uint32_t tNext = t + stride;
-        if (tNext < numTiles) {
-            nextI0 = plan.tileRow[tNext];
-            nextI1 = plan.tileRow[tNext + 1];
-            nextCls = plan.tileClass[tNext];
-        }
-        // Thread 0 refills this stage after the tile: its split points are fetched now.
-        const uint32_t tRefill = t + kStages * stride;
-        int refillI0 = 0, refillI1 = 0;
-        if (tid == 0 && tRefill < numTiles) {
-            refillI0 = plan.tileRow[tRefill];
-            refillI1 = plan.tileRow[tRefill + 1];
-        }
-        if (tid == 0) {
-            scratch.numLong = 0;
-            scratch.numWarpSeg = 0;
-        }
-        // A wait that runs out is recorded and the tile goes on with whatever the
-        // stage holds: indices are range-checked, so the worst outcome is a wrong
-        // value, and every thread keeps reaching the barriers below.
-        if (!waitedOut && !WaitStage(full + sIdx, parity)) {
-            waitedOut = true;  // and no further wait of this CTA is attempted
-        }
-
-        if (!g.valid) {
-            if (tid == 0) {
-                plan.carry[2 * t] = 0.0;
-                plan.carry[2 * t + 1] = 0.0;
-            }
-        } else {
-            float* sHi = stage;            // values, then the hi parts
-            float* sLo = stage + g.span;   // colInd, then the lo parts
-            int* sOff = reinterpret_cast<int*>(stage + 2 * g.span) + g.offShift;
-            float* sOut = stage + 2 * g.span + g.offWords;
-            for (int k = tid; k <= g.nr; k += kThreads) {
-                sOff[k] = ClampOffset(sOff[k], nnz) - g.j0;
-            }
-            const int nvec = g.span >> 2;
-            const int copied = g.copyElems >> 2;
-            struct Vec4 {
-                int4 c;
-                float4 w;
-            };
-            auto loadVec = [&](int v, Vec4& o) {
-                if (v < copied) {
-                    o.w = *reinterpret_cast<const float4*>(sHi + 4 * v);
-                    o.c = *reinterpret_cast<const int4*>(sLo + 4 * v);
-                } else {  // the last, partial vector of the arrays: plain loads
-                    const int e = g.a0 + 4 * v;
-                    int32_t c[4];
-                    float w[4];
-#pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        const bool in = e + q < nnz;
-                        c[q] = in ? __ldcs(colInd + e + q) : -1;
-                        w[q] = in ? __ldcs(values + e + q) : 0.0f;
-                    }
-                    o.c = make_int4(c[0], c[1], c[2], c[3]);
-                    o.w = make_float4(w[0], w[1], w[2], w[3]);
-                }
-            };
-            auto useVec = [&](int v, const Vec4& o) {
-                float4 hi, lo;
-                Product(o.w.x, o.c.x, x, p.indexBase, p.cols, 1, hi.x, lo.x);
-                Product(o.w.y, o.c.y, x, p.indexBase, p.cols, 1, hi.y, lo.y);
-                Product(o.w.z, o.c.z, x, p.indexBase, p.cols, 1, hi.z, lo.z);
-                Product(o.w.w, o.c.w, x, p.indexBase, p.cols, 1, hi.w, lo.w);
-                *reinterpret_cast<float4*>(sHi + 4 * v) = hi;
-                *reinterpret_cast<float4*>(sLo + 4 * v) = lo;
-            };
-            constexpr int kVecsPerThread = kTile / 4 / kThreads;
-            Vec4 vv[kVecsPerThread];
-#pragma unroll
-            for (int u = 0; u < kVecsPerThread; ++u) {
-                if (tid + u * kThreads < nvec) {
-                    loadVec(tid + u * kThreads, vv[u]);
-                }
-            }
-#pragma unroll
-            for (int u = 0; u < kVecsPerThread; ++u) {
-                if (tid + u * kThreads < nvec) {
-                    useVec(tid + u * kThreads, vv[u]);
-                }
-            }
-            for (int v = tid + kVecsPerThread * kThreads; v < nvec; v += kThreads) {
-                Vec4 vc;
-                loadVec(v, vc);
-                useVec(v, vc);
-            }
-            __syncthreads();
-
-            StagedTile st;
-            st.t = static_cast<int>(t);
-            st.i0 = g.i0;
-            st.i1 = g.i1;
-            st.nr = g.nr;
-            st.nt = g.nt;
-            st.cls = cls;
-            st.hiT = sHi + g.shift;
-            st.loT = sLo + g.shift;
-            st.sOff = sOff;
-            st.sOut = sOut;
-            ReduceTile(st, y, plan, p, scratch);
-        }
-        __syncthreads();  // the stage and the scratch are free
-        if (tid == 0 && tRefill < numTiles) {
-            // Shared-memory writes of the tile above come before the copy engine's writes.
-            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-            const TileGeom r = Geometry(tRefill, refillI0, refillI1, p);
-            IssueTile(r, stage, full + sIdx, colInd, values, plan.rowPtr, policy);
-        }
-    }
-    if (waitedOut) {
-        atomicAdd(waitFailures, 1u);
+// Lane 0: announce the bytes of a block to the stage's barrier and start its copies.
+__device__ __forceinline__ void IssueBlock(const RowBlockGeom& g, float* stage, int spanCap, uint64_t* bar,
+                                           const int32_t* colInd, const float* values, const int32_t* rowPtr,
+                                           uint64_t policy)
+{
+    const uint32_t arrayBytes = g.valid ? 4u * static_cast<uint32_t>(g.copyElems) : 0u;
+    const uint32_t offBytes = 4u * static_cast<uint32_t>(g.offWords);
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(SharedAddress(bar)),
+                 "r"(2u * arrayBytes + offBytes)
+                 : "memory");
+    BulkLoad(stage, rowPtr + g.r0, offBytes, bar, policy);
+    if (arrayBytes != 0) {
+        BulkLoad(stage + kOffsetWords, values + g.a0, arrayBytes, bar, policy);
+        BulkLoad(stage + kOffsetWords + spanCap, colInd + g.a0, arrayBytes, bar, policy);
     }
 }
 
-// One thread per tile whose first row began in an earlier tile and ends in
-// this one: adds the carry-outs of the tiles the row crossed, oldest first,
-// then the head partial, and writes the row.
-__global__ void SpmvCarryFixupKernel(float* __restrict__ y, SpmvPlanView plan, AclspSpmvParams p)
+// cap: longest row a stage can hold (the launcher sized shared memory for it).  kWarpsPerCta warps
+// per CTA, each with its own kStages stages; the launcher sizes the grid so that the stages of the
+// resident CTAs fill shared memory.  checkPlan != 0: return at once unless the plan header says that
+// no row is longer than cap (the host did not know yet which kernel the matrix needs).
+template <int kStages, int kWarpsPerCta, int kUnroll>
+__global__ void __launch_bounds__(32 * kWarpsPerCta)
+SpmvRowBlockKernel(const int32_t* __restrict__ colInd, const float* __restrict__ values, const float* __restrict__ x,
+                   float* __restrict__ y, SpmvPlanView plan, AclspSpmvParams p, const uint32_t* __restrict__ maxRowLen,
+                   uint32_t* __restrict__ waitFailures, int cap, int checkPlan)
 {
-    const uint32_t t = blockIdx.x * blockDim.x + threadIdx.x;
-    if (t >= plan.numTiles) {
-        return;
+    if (checkPlan != 0 && *maxRowLen > static_cast<uint32_t>(cap)) {
+        return;  // some row is too long for a stage: the merge-path tiles compute this product
     }
+    const int kSpanCap = RowBlockSpanCap(cap);
+    const int kWords = RowBlockStageWords(cap);
+    extern __shared__ __align__(128) unsigned char smemRaw[];
+    const int lane = threadIdx.x & 31;
+    const int warpInCta = threadIdx.x >> 5;
+    float* ring = reinterpret_cast<float*>(smemRaw) + static_cast<size_t>(warpInCta) * kStages * kWords;
+    uint64_t* full = reinterpret_cast<uint64_t*>(reinterpret_cast<float*>(smemRaw) +
+                                                 static_cast<size_t>(kWarpsPerCta) * kStages * kWords) +
+                     warpInCta * kStages;
+
     const int nnz = static_cast<int>(p.nnz);
-    const int i0 = plan.tileRow[t];
-    const int i1 = plan.tileRow[t + 1];
-    if (i1 <= i0 || i0 < 0 || i0 >= static_cast<int>(p.rows)) {
-        return;
+    const uint32_t numBlocks = (p.rows + kBlockRows - 1u) / kBlockRows;
+    const uint32_t totalWarps = gridDim.x * kWarpsPerCta;
+    const uint32_t firstBlock = blockIdx.x * kWarpsPerCta + warpInCta;
+    const uint64_t policy = EvictFirstPolicy();
+    const Scalars sc = LoadScalars(p);
+    const int32_t* rowPtr = plan.rowPtr;
+
+    auto lastRowOf = [&](uint32_t block) {
+        const uint32_t end = (block + 1u) * kBlockRows;
+        return end < p.rows ? end : p.rows;
+    };
+    if (lane == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(SharedAddress(full + s)) : "memory");
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+        uint32_t b = firstBlock;
+        for (int s = 0; s < kStages && b < numBlocks; ++s, b += totalWarps) {
+            const RowBlockGeom g = BlockGeometry(b, rowPtr[b * kBlockRows], rowPtr[lastRowOf(b)], p, kSpanCap);
+            IssueBlock(g, ring + s * kWords, kSpanCap, full + s, colInd, values, rowPtr, policy);
+        }
     }
+    __syncwarp();
+
+    // A row straight from global memory with fp64 products: the path of a warp whose wait ran
+    // out, and of blocks that do not fit a stage (row offsets that contradict the longest row the
+    // stages were sized for): slow, but right whatever the offsets and the hint are.
+    auto slowRow = [&](int row) {
+        const int b = ClampOffset(rowPtr[row], nnz);
+        const int e = ClampOffset(rowPtr[row + 1], nnz);
+        return ExactSum(colInd, values, x, b, e, 1, 1, 1, p.indexBase, p.cols);
+    };
+    auto writeRow = [&](int row, double sum) {
+        float* at = y + static_cast<int64_t>(row) * p.yStride;
+        const float out = StoreRow(at, 0, sum, sc);
+        if (p.numMirrors != 0) {
+            MirrorStore(at, out, p);  // 32 consecutive rows per warp: whole lines on the links
+        }
+    };
+
+    bool waitedOut = false;
+    uint32_t gaveUpAt = 0;
+    uint32_t it = 0;
+    // Extent of the block that refills the stage in use, loaded a turn ahead of its use.
+    int refillJ0 = 0, refillJ1 = 0;
+    for (uint32_t block = firstBlock; block < numBlocks; block += totalWarps, ++it) {
+        const int s = static_cast<int>(it % kStages);
+        const uint32_t parity = (it / kStages) & 1u;
+        float* stage = ring + s * kWords;
+        const uint32_t refill = block + kStages * totalWarps;
+        if (lane == 0 && refill < numBlocks && !waitedOut) {
+            refillJ0 = rowPtr[refill * kBlockRows];
+            refillJ1 = rowPtr[lastRowOf(refill)];
+        }
+        const int r0 = static_cast<int>(block) * kBlockRows;
+        const int row = r0 + lane;
+        const bool rowOk = row < static_cast<int>(p.rows);
+        if (!waitedOut) {
+            const bool landed = WaitStage(full + s, parity);
+            if (__any_sync(0xffffffffu, !landed)) {
+                waitedOut = true;
+                gaveUpAt = it;
+            }
+        }
+        if (waitedOut) {
+            if (rowOk) {
+                writeRow(row, slowRow(row));
+            }
+            continue;
+        }
+        const int* off = reinterpret_cast<const int*>(stage);
+        const RowBlockGeom g = BlockGeometry(block, off[0], off[lastRowOf(block) - r0], p, kSpanCap);
+        if (!g.valid) {
+            if (rowOk) {
+                writeRow(row, slowRow(row));
+            }
+        } else {
+            float* sVal = stage + kOffsetWords;
+            int* sCol = reinterpret_cast<int*>(stage + kOffsetWords + kSpanCap);
+            if (g.copyElems < g.span) {
+                // The arrays end inside this span with a partial vector: plain loads fill it.
+                for (int k = g.copyElems + lane; k < g.span; k += 32) {
+                    const int e = g.a0 + k;
+                    sCol[k] = e < nnz ? __ldcs(colInd + e) : -1;
+                    sVal[k] = e < nnz ? __ldcs(values + e) : 0.0f;
+                }
+                __syncwarp();
+            }
+            int b = 0, e = 0;
+            if (rowOk) {
+                b = ClampOffset(off[lane], nnz) - g.a0;
+                e = ClampOffset(off[lane + 1], nnz) - g.a0;
+                b = b < 0 ? 0 : (b > g.span ? g.span : b);
+                e = e < b ? b : (e > g.span ? g.span : e);
+            }
+            double h = 0.0;
+            float l = 0.0f;
+            int q = b;
+            // kUnroll products per lane and turn, all their gathers in flight together.
+            while (__any_sync(0xffffffffu, q < e)) {
+                int cc[kUnroll];
+                float vv[kUnroll];
+                float xx[kUnroll];
+#pragma unroll
+                for (int u = 0; u < kUnroll; ++u) {
+                    const bool ok = q + u < e;
+                    cc[u] = ok ? sCol[q + u] : -1;
+                    vv[u] = ok ? sVal[q + u] : 0.0f;
+                }
+#pragma unroll
+                for (int u = 0; u < kUnroll; ++u) {
+                    const uint32_t col = static_cast<uint32_t>(cc[u]) - p.indexBase;
+                    const bool in = col < p.cols;
+                    xx[u] = in ? __ldg(x + col) : 0.0f;
+                    vv[u] = in ? vv[u] : 0.0f;
+                }
+#pragma unroll
+                for (int u = 0; u < kUnroll; ++u) {
+                    const float hi = __fmul_rn(vv[u], xx[u]);
+                    l += fmaf(vv[u], xx[u], -hi);
+                    h += static_cast<double>(hi);
+                }
+                q += kUnroll;
+            }
+            if (rowOk) {
+                double sum = h + static_cast<double>(l);
+                if (!Finite(sum)) {
+                    sum = ExactSum(colInd, values, x, static_cast<int64_t>(g.a0) + b, static_cast<int64_t>(g.a0) + e, 1,
+                                   1, 1, p.indexBase, p.cols);
+                }
+                writeRow(row, sum);
+            }
+        }
+        __syncwarp();  // every lane is done with the stage
+        if (lane == 0 && refill < numBlocks) {
+            // Shared-memory reads of the block above come before the copy engine's writes.
+            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+            const RowBlockGeom r = BlockGeometry(refill, refillJ0, refillJ1, p, kSpanCap);
+            IssueBlock(r, stage, kSpanCap, full + s, colInd, values, rowPtr, policy);
+        }
+    }
+    if (waitedOut) {
+        // Copies started before the warp gave up may still land in its stages: each of them gets
+        // one more bounded wait before the warp, and with it perhaps the CTA, leaves.
+        for (uint32_t j = gaveUpAt; j < gaveUpAt + kStages; ++j) {
+            if (static_cast<uint64_t>(firstBlock) + static_cast<uint64_t>(j) * totalWarps < numBlocks) {
+                (void)WaitStage(full + j % kStages, (j / kStages) & 1u);
+            }
+        }
+        if (lane == 0) {
+            atomicAdd(waitFailures, 1u);
+        }
+    }
+}
+
+/* ----------------------------------------------------- carry fix-up -- */
+
+// Rows that span tiles.  A warp looks at 32 tiles, one per lane: tile t needs a fix-up when its
+// first row began in an earlier tile and ends in t.  The warp then takes those tiles one by one:
+// the lanes add the carry-outs of the tiles the row crossed (lane-strided, then a shuffle tree: a
+// fixed order), lane 0 adds the head partial and writes the row.
+__global__ void __launch_bounds__(kThreads)
+SpmvCarryFixupKernel(float* __restrict__ y, SpmvPlanView plan, AclspSpmvParams p, const uint32_t* __restrict__ maxRowLen,
+                     uint32_t rowBlockCap)
+{
+    if (rowBlockCap != 0 && *maxRowLen <= rowBlockCap) {
+        return;  // the row-block kernel computed this product: there are no carries
+    }
+    const int lane = threadIdx.x & 31;
+    const uint32_t warp = blockIdx.x * kWarps + (threadIdx.x >> 5);
+    const uint32_t t = warp * 32u + lane;
+    const int nnz = static_cast<int>(p.nnz);
     const int64_t total = static_cast<int64_t>(p.rows) + nnz;
-    int64_t d0 = static_cast<int64_t>(t) * kTile;
-    d0 = d0 < total ? d0 : total;
-    const int64_t j0 = d0 - i0;
-    if (ClampOffset(plan.rowPtr[i0], nnz) >= j0) {
-        return;
+    bool needs = false;
+    int i0 = 0;
+    if (t < plan.numTiles) {
+        i0 = plan.tileRow[t];
+        const int i1 = plan.tileRow[t + 1];
+        if (i1 > i0 && i0 >= 0 && i0 < static_cast<int>(p.rows)) {
+            int64_t d0 = static_cast<int64_t>(t) * kTile;
+            d0 = d0 < total ? d0 : total;
+            needs = ClampOffset(plan.rowPtr[i0], nnz) < d0 - i0;
+        }
     }
-    uint32_t first = t;
-    while (first > 0 && plan.tileRow[first] == i0) {
-        --first;
+    uint32_t todo = __ballot_sync(0xffffffffu, needs);
+    const Scalars sc = LoadScalars(p);
+    while (todo != 0) {
+        const int src = __ffs(todo) - 1;
+        todo &= todo - 1;
+        const uint32_t tt = warp * 32u + src;
+        const int row = __shfl_sync(0xffffffffu, i0, src);
+        // Tiles first .. tt-1 hold the earlier pieces of the row: `first` is the last tile that
+        // starts at a row before it (tileRow is non-decreasing), or tile 0.
+        uint32_t lo = 0;
+        uint32_t hi = tt;
+        while (lo < hi) {
+            const uint32_t mid = (lo + hi) >> 1;
+            if (plan.tileRow[mid] < row) {
+                lo = mid + 1;
+            } else {
+                hi = mid;
+            }
+        }
+        const uint32_t first = lo > 0 ? lo - 1 : 0;
+        double sum = 0.0;
+        for (uint32_t u = first + lane; u < tt; u += 32) {
+            sum += plan.carry[2 * u];
+        }
+        for (int o = 16; o > 0; o >>= 1) {
+            sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        }
+        if (lane == 0) {
+            sum += plan.carry[2 * tt + 1];
+            float* at = y + static_cast<int64_t>(row) * p.yStride;
+            const float out = StoreRow(at, 0, sum, sc);
+            if (p.numMirrors != 0) {
+                MirrorStore(at, out, p);
+            }
+        }
     }
-    double sum = 0.0;
-    for (uint32_t u = first; u < t; ++u) {
-        sum += plan.carry[2 * u];
+}
+
+int EnvInt(const char* name, int fallback)
+{
+    const char* e = std::getenv(name);
+    return e == nullptr ? fallback : std::atoi(e);
+}
+
+void LaunchRowBlocks(const void* colInd, const void* values, const void* x, void* y, const SpmvPlanView& plan,
+                     const AclspSpmvParams& p, const uint32_t* maxRowLen, uint32_t* waitFailures, int cap, bool checkPlan,
+                     cudaStream_t s)
+{
+    constexpr int kStages = 1;
+    constexpr int kWarpsPerCta = 2;
+    constexpr int kUnroll = 16;
+    int device = 0;
+    int sms = 0;
+    if (cudaGetDevice(&device) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms <= 0) {
+        sms = 148;
     }
-    sum += plan.carry[2 * t + 1];
-    float* at = y + static_cast<int64_t>(i0) * p.yStride;
-    const float out = StoreRow(at, 0, sum, LoadScalars(p));
-    if (p.numMirrors != 0) {
-        MirrorStore(at, out, p);
-    }
+    const size_t smem = sizeof(float) * kWarpsPerCta * kStages * RowBlockStageWords(cap) +
+                        sizeof(uint64_t) * kWarpsPerCta * kStages;
+    auto kernel = SpmvRowBlockKernel<kStages, kWarpsPerCta, kUnroll>;
+    cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    // Resident CTAs per SM: what shared memory holds (a CTA also takes 1 KiB of system shared memory),
+    // at most 32 CTAs and 32 warps of this register footprint.
+    uint32_t ctasPerSm = static_cast<uint32_t>((220u * 1024u) / (smem + 1024u));
+    ctasPerSm = ctasPerSm > 32u / kWarpsPerCta ? 32u / kWarpsPerCta : (ctasPerSm > 0 ? ctasPerSm : 1u);
+    const uint32_t numBlocks = (p.rows + kBlockRows - 1u) / kBlockRows;
+    uint32_t grid = static_cast<uint32_t>(sms) * ctasPerSm;
+    const uint32_t needed = (numBlocks + kWarpsPerCta - 1u) / kWarpsPerCta;
+    grid = grid < needed ? grid : needed;
+    kernel<<<grid > 0 ? grid : 1u, 32 * kWarpsPerCta, smem, s>>>(
+        static_cast<const int32_t*>(colInd), static_cast<const float*>(values), static_cast<const float*>(x),
+        static_cast<float*>(y), plan, p, maxRowLen, waitFailures, cap, checkPlan ? 1 : 0);
 }
 
 }  // namespace
@@ -854,41 +992,47 @@ extern "C" void spmv_b200_kernel_do(const void* colInd, const void* values, cons
     }
     const bool vector = p.colIndStride == 1 && p.valuesStride == 1 && p.xStride == 1 &&
                         reinterpret_cast<uintptr_t>(colInd) % 16 == 0 && reinterpret_cast<uintptr_t>(values) % 16 == 0;
-    // ACLSPARSE_SPMV_STREAM=1 selects the persistent bulk-copy kernel.  It needs 16-byte aligned sources
-    // for its copies: the CSR arrays (as the vector path does) and the row offsets inside the plan.
-    static const bool streamEnv = [] {
-        const char* e = std::getenv("ACLSPARSE_SPMV_STREAM");
-        return e != nullptr && e[0] == '1';
-    }();
-    const bool streamed = vector && streamEnv && reinterpret_cast<uintptr_t>(plan.rowPtr) % 16 == 0;
-    if (streamed) {
-        int device = 0;
-        int sms = 0;
-        if (cudaGetDevice(&device) != cudaSuccess ||
-            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms <= 0) {
-            sms = 148;
+    auto* header = static_cast<unsigned char*>(workspace);
+    const auto* maxRowLen = reinterpret_cast<const uint32_t*>(header + ACLSP_HEADER_MAX_ROW_LEN_OFF);
+    auto* waitFailures = reinterpret_cast<uint32_t*>(header + ACLSP_HEADER_WAIT_FAILURES_OFF);
+    // The row-block kernel needs unit strides and 16-byte aligned sources for its bulk copies (the CSR
+    // arrays and the row offsets inside the plan), and a stage that holds the longest row.  It pays when
+    // rows are short and of similar length, i.e. when the longest row is not much longer than the mean.
+    // ACLSPARSE_SPMV_ROW_BLOCKS=0 switches the row-block kernel off (a debugging aid, read once).
+    static const int rowBlocksEnv = EnvInt("ACLSPARSE_SPMV_ROW_BLOCKS", 1);
+    const bool eligible = vector && rowBlocksEnv != 0 && reinterpret_cast<uintptr_t>(plan.rowPtr) % 16 == 0 &&
+                          p.rows > 0 && p.nnz > 0;
+    uint32_t cap = 0;         // != 0: launch the row-block kernel with stages for rows of this length
+    bool checkPlan = false;   // the kernels decide by the plan header which of them computes
+    if (eligible && p.maxRowLenHint != ACLSP_MAX_ROW_LEN_UNKNOWN) {
+        // The longest row is known: exactly one kernel is launched.
+        const uint64_t longest = p.maxRowLenHint;
+        if (longest <= static_cast<uint64_t>(kRowBlockMaxLen) && longest * p.rows <= 3ull * p.nnz + p.rows) {
+            cap = static_cast<uint32_t>(longest > 0 ? longest : 1u);
         }
-        auto* waitFailures =
-            reinterpret_cast<uint32_t*>(static_cast<unsigned char*>(workspace) + ACLSP_HEADER_WAIT_FAILURES_OFF);
-        auto launch = [&](auto kernel, int stages, int ctas) {
-            const size_t smem = sizeof(float) * stages * kStageWords + sizeof(uint64_t) * stages + sizeof(ReduceScratch);
-            cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-            const uint32_t resident = static_cast<uint32_t>(sms) * ctas;
-            const uint32_t grid = plan.numTiles < resident ? plan.numTiles : resident;
-            kernel<<<grid, kThreads, smem, s>>>(static_cast<const int32_t*>(colInd), static_cast<const float*>(values),
-                                                static_cast<const float*>(x), static_cast<float*>(y), plan, p,
-                                                waitFailures);
-        };
-        // Also measured: 2 stages with 5 / 6 CTAs per SM (48 / 40 registers): 0.344 / 0.381 ms on the stencil.
-        launch(SpmvStreamKernel<kStreamStages, kStreamCtasPerSm>, kStreamStages, kStreamCtasPerSm);
-    } else if (vector) {
+    } else if (eligible) {
+        // Not known yet: guess from the mean row length, launch both, let the plan header decide.
+        const uint64_t mean8 = (8ull * p.nnz + p.rows - 1u) / p.rows;  // mean row length, in eighths, rounded up
+        cap = mean8 <= 8u * 14u ? 16u : (mean8 <= 8u * 28u ? 32u : 0u);
+        checkPlan = cap != 0;
+    }
+    if (cap != 0) {
+        LaunchRowBlocks(colInd, values, x, y, plan, p, maxRowLen, waitFailures, static_cast<int>(cap), checkPlan, s);
+        if (!checkPlan) {
+            return;
+        }
+    }
+    const uint32_t tileCap = checkPlan ? cap : 0u;
+    if (vector) {
         SpmvTileKernel<true><<<plan.numTiles, kThreads, 0, s>>>(
             static_cast<const int32_t*>(colInd), static_cast<const float*>(values), static_cast<const float*>(x),
-            static_cast<float*>(y), plan, p);
+            static_cast<float*>(y), plan, p, maxRowLen, tileCap);
     } else {
         SpmvTileKernel<false><<<plan.numTiles, kThreads, 0, s>>>(
             static_cast<const int32_t*>(colInd), static_cast<const float*>(values), static_cast<const float*>(x),
-            static_cast<float*>(y), plan, p);
+            static_cast<float*>(y), plan, p, maxRowLen, tileCap);
     }
-    SpmvCarryFixupKernel<<<(plan.numTiles + 255u) / 256u, 256, 0, s>>>(static_cast<float*>(y), plan, p);
+    const uint32_t fixupWarps = (plan.numTiles + 31u) / 32u;
+    SpmvCarryFixupKernel<<<(fixupWarps + kWarps - 1u) / kWarps, kThreads, 0, s>>>(static_cast<float*>(y), plan, p,
+                                                                                 maxRowLen, tileCap);
 }

@@ -119,6 +119,7 @@ extern "C" aclsparseStatus_t aclsparseB200SpMVNoAlloc(aclrtStream stream, int64_
     params.yStride = 1;
     params.alpha = alpha;
     params.beta = beta;
+    params.maxRowLenHint = ACLSP_MAX_ROW_LEN_UNKNOWN;  // the plan was built a moment ago: the kernels decide
 
     (void)cudaGetLastError();
     spmv_b200_preprocess_kernel_do(rowOffsets, scratch, params.rows, params.cols, params.nnz,

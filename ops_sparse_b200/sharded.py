@@ -143,7 +143,9 @@ class _GraphedStep:
     """
 
     _graph = None
+    _product_graph = None
     _out = None
+    _group = None
 
     def reassemble_in_kernel(self, on: bool) -> None:
         """Registers (or clears) the other ranks' buffers as mirrors of the local output (fused / multicast)."""
@@ -156,24 +158,80 @@ class _GraphedStep:
         else:
             self._out.set_mirrors(self.gather.mirror_ptrs)
 
-    def capture(self, alpha: float, beta: float) -> bool:
-        """Records ``step(alpha, beta)`` into a graph that later ``step`` calls with the same scalars replay."""
-        if self._product is not None or (self.world > 1 and self.gather_mode == "nccl"):
-            return False
+    def _capture(self, body):
         side = torch.cuda.Stream(device=self.device)
         side.wait_stream(torch.cuda.current_stream())
         self.handle.set_stream(side.cuda_stream)
         try:
             with torch.cuda.stream(side):
-                self._eager_step(alpha, beta)  # first use on this stream: nothing lazy is left for the capture
+                body()  # first use on this stream: nothing lazy is left for the capture
             side.synchronize()
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, stream=side):
-                self._eager_step(alpha, beta)
+                body()
         finally:
             self.handle.set_stream(torch.cuda.current_stream().cuda_stream)
-        self._graph = (graph, float(alpha), float(beta))
+        return graph
+
+    def capture(self, alpha: float, beta: float) -> bool:
+        """Records ``step(alpha, beta)`` into a graph that later ``step`` calls with the same scalars replay."""
+        if self._product is not None or (self.world > 1 and self.gather_mode == "nccl"):
+            return False
+        self._graph = (self._capture(lambda: self._eager_step(alpha, beta)), float(alpha), float(beta))
         return True
+
+    def capture_product(self, alpha: float, beta: float):
+        """The local product alone (no reassembly step) as a graph; returns a callable that replays it."""
+        if self._product is not None or self.r1 <= self.r0:
+            return None
+        graph = self._capture(lambda: self.op(alpha, beta))
+        self._product_graph = graph  # kept alive with the operator
+        return graph.replay
+
+    # ---- what the benchmark reports about the operator
+    def launches_per_step(self) -> int:
+        """Kernels of this library launched per step on this rank (kernels that find nothing to do included)."""
+        n = len(self.kernel_names.split(" + ")) if self.r1 > self.r0 else 0
+        if self.world > 1 and self.gather_mode != "nccl":
+            n += 1 if self.gather_mode in ("fused", "multicast") else 2  # the barrier kernel (+ the push kernel)
+        return n
+
+    # ---- inputs that arrive from the host: every rank uploads one share, the shares are all-gathered
+    def pinned_input_share(self, cfg: dict) -> torch.Tensor:
+        """This rank's share of x (or of the rows of B) in pinned host memory, padded to the common share size."""
+        src = torch.from_numpy(cfg["x"] if self.kind == "spmv" else cfg["b"])
+        lo = min(self.rank * self._share, src.shape[0])
+        hi = min(lo + self._share, src.shape[0])
+        out = torch.zeros((self._share,) + tuple(src.shape[1:]), dtype=torch.float32).pin_memory()
+        out[: hi - lo].copy_(src[lo:hi])
+        return out
+
+    def load_input_share(self, host_share: torch.Tensor) -> None:
+        """Host -> device copy of this rank's share, then the all-gather that completes every replica."""
+        lo = self.rank * self._share
+        mine = self._input_pad[lo:lo + self._share]
+        mine.copy_(host_share, non_blocking=True)
+        if self.world > 1:
+            dist.all_gather_into_tensor(self._input_pad.view(-1), mine.reshape(-1), group=self._group)
+
+    def _make_input(self, full: np.ndarray, device) -> torch.Tensor:
+        """Replica of x / B inside a buffer padded to world_size equal shares; returns the unpadded view."""
+        rows = full.shape[0]
+        self._share = (rows + self.world - 1) // self.world
+        self._input_pad = torch.zeros((self._share * self.world,) + tuple(full.shape[1:]), dtype=torch.float32,
+                                      device=device)
+        view = self._input_pad[:rows]
+        view.copy_(torch.from_numpy(full))
+        return view
+
+    def close(self) -> None:
+        """Drops graphs, descriptors and device arrays (the benchmark measures several operators in one process)."""
+        self._graph = None
+        self._product_graph = None
+        for name in ("op", "mat", "handle", "gather", "d_ptr", "d_col", "d_val", "x", "b", "y_local", "c_local",
+                     "_input_pad", "_out"):
+            if hasattr(self, name):
+                setattr(self, name, None)
 
     def step(self, alpha: float, beta: float) -> torch.Tensor:
         """One product: local row block, then the reassembly; returns the full result (identical on every rank)."""
@@ -192,14 +250,17 @@ class ShardedSpMV(_GraphedStep):
     """
 
     def __init__(self, cfg: dict, rank: int, world: int, device, group=None, local_product=None, gather="multicast"):
-        self.rank, self.world, self.device = rank, world, device
+        self.rank, self.world, self.device, self._group = rank, world, device, group
+        self.kind = "spmv"
+        self.algorithm = "exact fp32 products (hi + lo), fp64 row sums"
+        self.kernel_names = "SpmvRowBlockKernel + SpmvTileKernel + SpmvCarryFixupKernel"
         base = cfg.get("index_base", 0)
         self.bounds = row_block_bounds_host(cfg["row_ptr"], cfg["nnz"], world, base)
         self.local_ptr, self.local_col, self.local_val = shard_csr(cfg["row_ptr"], cfg["col_ind"], cfg["values"],
                                                                    self.bounds, rank, base)
         self.r0, self.r1 = int(self.bounds[rank]), int(self.bounds[rank + 1])
         self.gather, self.gather_mode = _make_gather(gather, self.bounds, rank, 1, device, group)
-        self.x = torch.from_numpy(cfg["x"]).to(device)
+        self.x = self._make_input(cfg["x"], device)
         self.y_local = self.gather.local
         self.y_local.copy_(torch.from_numpy(cfg["y"][self.r0:self.r1]).to(device))
         self._product = local_product
@@ -229,8 +290,12 @@ class ShardedSpMV(_GraphedStep):
 class ShardedSpMM(_GraphedStep):
     """C = alpha * A * B + beta * C (row-major B and C) with A row-block sharded over the ranks."""
 
-    def __init__(self, cfg: dict, rank: int, world: int, device, group=None, local_product=None, gather="multicast"):
-        self.rank, self.world, self.device = rank, world, device
+    def __init__(self, cfg: dict, rank: int, world: int, device, group=None, local_product=None, gather="multicast",
+                 alg: int = L.SPMM_ALG_DEFAULT):
+        self.rank, self.world, self.device, self._group = rank, world, device, group
+        self.kind = "spmm"
+        self.algorithm = "fp64 products, fp64 row sums (every algorithm value)"
+        self.kernel_names = "SpmmTileKernel + SpmmCarryFixupKernel"
         base = cfg.get("index_base", 0)
         n = cfg["n"]
         self.bounds = row_block_bounds_host(cfg["row_ptr"], cfg["nnz"], world, base)
@@ -238,7 +303,7 @@ class ShardedSpMM(_GraphedStep):
                                                                    self.bounds, rank, base)
         self.r0, self.r1 = int(self.bounds[rank]), int(self.bounds[rank + 1])
         self.gather, self.gather_mode = _make_gather(gather, self.bounds, rank, n, device, group)
-        self.b = torch.from_numpy(cfg["b"]).to(device)
+        self.b = self._make_input(cfg["b"], device)
         self.c_local = self.gather.local
         self.c_local.copy_(torch.from_numpy(cfg["c"][self.r0:self.r1]).to(device))
         self._product = local_product
@@ -253,7 +318,7 @@ class ShardedSpMM(_GraphedStep):
                                      nnz=int(self.local_col.size))
             if rows > 0:
                 self.op = api.SpMM(self.handle, self.mat, api.DnMat(cfg["cols"], n, n, self.b),
-                                   api.DnMat(rows, n, n, self.c_local))
+                                   api.DnMat(rows, n, n, self.c_local), alg=alg)
                 self._out = self.op.c
                 self.reassemble_in_kernel(True)
                 self.op.preprocess()

@@ -217,6 +217,12 @@ def plan_header(kind: int, rows: int, cols: int, nnz: int, index_base: int, dens
     return np.concatenate([head.view(np.uint8), tail.view(np.uint8)])
 
 
+def longest_row(row_ptr) -> int:
+    """Longest row as the SpMV preprocessing pass records it in the plan header (a negative length counts as 0)."""
+    d = np.diff(np.asarray(row_ptr, dtype=np.int64))
+    return int(max(d.max(), 0)) if d.size else 0
+
+
 def row_block_bounds(row_ptr, nnz: int, parts: int, index_base=0) -> np.ndarray:
     row_ptr = _i32(row_ptr)
     bounds = np.empty(parts + 1, dtype=np.int32)

@@ -57,6 +57,34 @@ def test_without_preprocess_and_rebinding(kats):
     np.testing.assert_allclose(case.run(preprocess=False), [4, 2], atol=1e-5)
 
 
+def test_two_matrices_sharing_one_workspace():
+    """A1, A2, A1 through one external buffer: every product uses its own matrix's plan, with and without
+    explicit Preprocess calls (two matrices of equal rows and nnz, so that their plans have the same layout)."""
+    rng = np.random.default_rng(31)
+    rows, cols = 6000, 5000
+    lens1 = rng.integers(0, 40, rows)
+    lens2 = rng.permutation(lens1)                 # same rows and nnz, different structure
+    x = rng.standard_normal(cols).astype(np.float32)
+    y0 = np.zeros(rows, np.float32)
+    mats = []
+    for lens in (lens1, lens2):
+        rp, ci = random_csr(rng, lens, cols)
+        va = rng.standard_normal(ci.size).astype(np.float32)
+        mats.append((rp, ci, va, O.spmv_f64(rp, ci, va, x, y0)))
+    h = api.Handle()
+    cases = [SpmvCase(rp, ci, va, x, y0, handle=h) for rp, ci, va, _ in mats]
+    shared = cases[0].op.allocate()
+    cases[1].op.buffer = shared
+    for preprocess in (True, False):
+        if preprocess:
+            cases[0].op.preprocess()
+            cases[1].op.preprocess()               # overwrites the plan of the first matrix
+        for which in (0, 1, 0, 0, 1):
+            cases[which].d_y.zero_()
+            got = cases[which].run(1.0, 0.0, preprocess=False)
+            assert_close(got, mats[which][3], f"matrix {which}, preprocess={preprocess}")
+
+
 def test_beta_zero_never_reads_y():
     rng = np.random.default_rng(1)
     rp, ci = random_csr(rng, rng.integers(0, 40, 3000), 2500)
@@ -92,16 +120,18 @@ def test_benchmark_configs_vs_oracle(name, rows):
         assert np.array_equal(again.view(np.uint32), got.view(np.uint32))
 
 
-def test_both_kernels_give_the_same_bits_and_no_wait_runs_out():
-    """The persistent bulk-copy kernel and the one-CTA-per-tile kernel reduce in the same order: equal bits.
-    The persistent kernel (opt-in) counts bounded waits that ran out in the plan header; the count stays 0."""
+def test_both_kernels_agree_and_no_wait_runs_out():
+    """Matrices with short rows are computed by the row-block kernel, or by the merge-path tile kernel when
+    it is switched off (ACLSPARSE_SPMV_ROW_BLOCKS=0): both meet the tolerance against the oracle.  The
+    row-block kernel counts bounded waits that ran out in the plan header; the count stays 0."""
     import subprocess, sys, os
+    shapes = (("c1", None), ("c2", 50 ** 3), ("c3", 1 << 16))
     code = (
         "import sys, numpy as np, torch; sys.path.insert(0, %r); sys.path.insert(0, %r)\n"
         "from gpu_util import SpmvCase\n"
         "from ops_sparse_b200 import workloads\n"
         "out = []\n"
-        "for name, rows in (('c1', None), ('c2', 50 ** 3), ('c3', 1 << 16)):\n"
+        "for name, rows in " + repr(shapes) + ":\n"
         "    cfg = workloads.make(name, rows=rows)\n"
         "    case = SpmvCase(cfg['row_ptr'], cfg['col_ind'], cfg['values'], cfg['x'], cfg['y'])\n"
         "    got = case.run(cfg['alpha'], cfg['beta'])\n"
@@ -111,14 +141,18 @@ def test_both_kernels_give_the_same_bits_and_no_wait_runs_out():
         "np.save(sys.argv[1], np.concatenate(out))\n"
     ) % (os.path.dirname(os.path.abspath(__file__)), os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
     import tempfile
-    results = {}
+    truth = []
+    for name, rows in shapes:
+        cfg = workloads.make(name, rows=rows)
+        truth.append(O.spmv_f64(cfg["row_ptr"], cfg["col_ind"], cfg["values"], cfg["x"], cfg["y"], cfg["alpha"],
+                                cfg["beta"], threads=O.max_threads()))
+    truth = np.concatenate(truth)
     for mode in ("1", "0"):  # the choice is read once per process
         with tempfile.TemporaryDirectory() as tmp:
             path = os.path.join(tmp, "y.npy")
-            env = dict(os.environ, ACLSPARSE_SPMV_STREAM=mode)
+            env = dict(os.environ, ACLSPARSE_SPMV_ROW_BLOCKS=mode)
             subprocess.run([sys.executable, "-c", code, path], check=True, env=env, timeout=600)
-            results[mode] = np.load(path)
-    assert np.array_equal(results["1"].view(np.uint32), results["0"].view(np.uint32))
+            assert_close(np.load(path), truth, f"ACLSPARSE_SPMV_ROW_BLOCKS={mode}")
 
 
 def test_plan_metadata_bit_exact():
@@ -144,6 +178,9 @@ def test_plan_metadata_bit_exact():
             rows = len(lengths)
             got_rp = ws[lay["row_ptr_off"]:lay["row_ptr_off"] + 4 * (rows + 1)].view(np.int32)
             assert np.array_equal(got_rp, O.normalize_row_offsets(rp + base, rows, base))
+            # the counters behind the header: no bounded wait ran out; the longest row
+            assert ws[128:132].view(np.uint32)[0] == 0
+            assert ws[132:136].view(np.uint32)[0] == O.longest_row(rp + base)
             tile_row, tile_class = O.plan_tiles(rp, nnz, O.SPMV_TILE_ITEMS, O.SPMV_CLASS_DIV)
             nt = lay["num_tiles"]
             assert np.array_equal(ws[lay["tile_row_off"]:lay["tile_row_off"] + 4 * (nt + 1)].view(np.int32), tile_row)
@@ -175,6 +212,60 @@ def test_long_rows_and_mixed_tiles():
     y = rng.uniform(-1, 1, lengths.size).astype(np.float32)
     got = SpmvCase(rp, ci, va, x, y).run(-0.75, 1.25)
     assert_close(got, O.spmv_f64(rp, ci, va, x, y, -0.75, 1.25), "long rows")
+
+
+def assert_matches_f64_golden(got, truth, what=""):
+    """fp32 result against the fp64 golden rounded to fp32: NaN where it is NaN, the same infinity where it is
+    infinite, within the tolerance everywhere else."""
+    with np.errstate(over="ignore", invalid="ignore"):
+        want = truth.astype(np.float32)
+    assert np.array_equal(np.isnan(got), np.isnan(want)), f"{what}: NaN pattern {got} vs {want}"
+    inf = np.isinf(want)
+    assert np.array_equal(got[inf], want[inf]), f"{what}: infinities {got[inf]} vs {want[inf]}"
+    fin = np.isfinite(want)
+    assert_close(got[fin], truth[fin], what)
+
+
+def test_extreme_and_non_finite_values():
+    """The reference's extreme-value regression (test/spmv/arch22/spmv_test.cpp:1923-1936: 2^116 and 1e35 entries,
+    alpha = 2^-116), fp32 products that overflow while the fp64 sum is finite, and Inf / NaN in A and in x, in short
+    rows (row-block kernel) and in rows that span tiles (merge-path kernel): all equal to the fp64 golden."""
+    rng = np.random.default_rng(21)
+    rp = np.array([0, 1, 3, 3, 5], np.int32)
+    ci = np.array([0, 1, 7, 2, 5], np.int32)
+    va = np.array([2.0 ** 116, 1.0e35, 2.0, 1.0e35, -3.0], np.float32)
+    x = rng.uniform(-5, 5, 8).astype(np.float32)
+    y = np.zeros(4, np.float32)
+    alpha = float(2.0 ** -116)
+    got = SpmvCase(rp, ci, va, x, y).run(alpha, 0.0)
+    assert_matches_f64_golden(got, O.spmv_f64(rp, ci, va, x, y, alpha, 0.0), "extreme-large-val")
+
+    big = np.float32(3.0e38)
+    for long_len in (0, 6000):  # 0: short rows only; 6000: one row over three tiles in front of them
+        rows_v = [[big, -big, 1.0], [big, 2.0], [np.inf, 1.0, 1.0], [-np.inf, 1.0], [np.inf, -np.inf], [np.nan, 1.0],
+                  [1.0, 2.0, 3.0], [0.0, 5.0], [1.0, 1.0]]
+        rows_x = [[2.0, 2.0, 1.0], [2.0, 1.0], [1.0, 1.0, 1.0], [2.0, 1.0], [1.0, 1.0], [1.0, 1.0],
+                  [np.inf, 1.0, 1.0], [np.inf, 1.0], [np.nan, 1.0]]
+        if long_len:
+            # The overflowing pair leads the row: the golden adds in array order, and a 6e38 term met later
+            # would swallow whatever it had summed before, which is an artefact of that order, not the product.
+            lv = rng.standard_normal(long_len).astype(np.float32)
+            lx = rng.standard_normal(long_len).astype(np.float32)
+            lv[0], lv[1], lx[0], lx[1] = big, -big, 2.0, 2.0   # cancels in fp64, overflows in fp32
+            li = lv.copy()
+            li[4000] = np.inf                                   # a row over three tiles that is +Inf
+            rows_v, rows_x = [list(lv)] + rows_v + [list(li)], [list(lx)] + rows_x + [list(np.abs(lx) + 1)]
+        # every entry gets its own column, so that x can hold the factor meant for it
+        lens = [len(r) for r in rows_v]
+        rp = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+        nnz = int(rp[-1])
+        ci = np.arange(nnz, dtype=np.int32)
+        va = np.concatenate(rows_v).astype(np.float32)
+        x = np.concatenate(rows_x).astype(np.float32)
+        y = np.ones(len(lens), np.float32)
+        for a, b in ((1.0, 0.0), (0.5, 2.0)):
+            got = SpmvCase(rp, ci, va, x, y).run(a, b)
+            assert_matches_f64_golden(got, O.spmv_f64(rp, ci, va, x, y, a, b), f"non-finite long={long_len} {a},{b}")
 
 
 def test_strided_storage_preserves_padding():
