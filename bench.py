@@ -58,7 +58,11 @@ FALLBACK_HBM_GBS = 6650.0
 # DRAM read + write bytes per algorithmic byte, from ncu captures of the kernels named (profiles/):
 # SpMV traffic is proportional to the algorithmic bytes, so a 1 M-row capture scales; the SpMM figures
 # are from one full-size launch each.
-TRAFFIC_RATIO = {}
+TRAFFIC_RATIO = {
+    "c2": 224.06 / 223.71,   # SpmvRowBlockKernel, 1 M-row stencil
+    "c3": 273.9 / 272.24,    # SpmvTileKernel, 1 M-row power-law case
+    "c4": 7.972 / 1.2122,    # SpmmTileKernel, one full-size launch
+}
 
 
 def measured_peak():
@@ -450,7 +454,7 @@ def run_ours(args):
             continue
         other = workloads.make(name, rows=args.rows if args.rows is not None and name != "c1" else None)
         steps = args.steps if other["kind"] == "spmv" else max(3, min(args.steps, 10))
-        configs[name] = measure(ctx, args, other, steps, max(3, args.warmup), 0.0)
+        configs[name] = measure(ctx, args, other, steps, max(3, args.warmup), 0.25)
         del other
         gc.collect()
 

@@ -58,6 +58,20 @@ aclsparseStatus_t aclsparseB200DnMatSetMirrors(aclsparseDnMatDescr_t mat, int co
 aclsparseStatus_t aclsparseB200DnVecSetMulticastMirror(aclsparseDnVecDescr_t vec, void* multicast);
 aclsparseStatus_t aclsparseB200DnMatSetMulticastMirror(aclsparseDnMatDescr_t mat, void* multicast);
 
+/* Barrier across the GPUs of a node that share a row-block-sharded result: enqueues, on `stream`, one
+ * small kernel that tells every peer "my row block is in your buffer" and waits until every peer has said
+ * the same.  `localState` is this rank's AclspNodeBarrierState (aclsparse_b200_kernels.h; 128 bytes of
+ * zero-filled memory that all ranks can address), `peerStates[r]` rank r's as this device addresses it.
+ * The wait is bounded by `spinLimit` polls per peer (0 picks the default, about a second): a peer that
+ * never arrives makes the kernel give up and record it, nothing hangs and nothing traps.
+ * aclsparseB200NodeBarrierStatus synchronises `stream`, reads that record and clears it: it returns
+ * ACL_SPARSE_STATUS_EXECUTION_FAILED when a barrier since the last call gave up (and, if `missingRank` is
+ * non-null, stores the rank that was missing), ACL_SPARSE_STATUS_SUCCESS otherwise.
+ * No counterpart in the reference, which is single-device. */
+aclsparseStatus_t aclsparseB200NodeBarrier(aclrtStream stream, void* localState, void* const* peerStates, int world,
+                                           int rank, unsigned spinLimit);
+aclsparseStatus_t aclsparseB200NodeBarrierStatus(aclrtStream stream, void* localState, int* missingRank);
+
 #ifdef __cplusplus
 }
 #endif

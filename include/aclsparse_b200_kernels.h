@@ -119,6 +119,26 @@ void aclsp_b200_row_block_bounds_kernel_do(const void* rowPtr, uint32_t rows, ui
 void aclsp_b200_push_slice_kernel_do(const void* src, void* const* peers, uint32_t numPeers, int64_t offsetElems,
                                      int64_t countElems, void* stream);
 
+/* State of the node barrier, one per rank, in memory that every rank of the node can address (peer-mapped /
+ * symmetric memory), zero-filled before the first barrier.  epoch: barriers this rank has entered.
+ * status: 0, or 1 + the rank that did not arrive within the limit of some barrier since the host last
+ * looked.  flag[r]: the epoch rank r has announced to this rank. */
+#define ACLSP_BARRIER_MAX_RANKS 16
+typedef struct AclspNodeBarrierState {
+    uint32_t epoch;
+    uint32_t status;
+    uint32_t reserved[2];
+    uint32_t flag[ACLSP_BARRIER_MAX_RANKS];
+} AclspNodeBarrierState;
+
+/* One barrier across `world` (2..16) ranks: announces this rank's next epoch in every peer's state, then
+ * waits, at most `spinLimit` polls per peer (a poll is a fraction of a microsecond), until every peer has
+ * announced it too; a wait that runs out sets localState->status and the kernel returns.  peerStates is a
+ * host array of `world` device pointers, entry r being rank r's state as this device addresses it (entry
+ * `rank` is unused).  One warp, one launch.  No counterpart in the reference, which is single-device. */
+void aclsp_b200_node_barrier_kernel_do(void* localState, void* const* peerStates, uint32_t world, uint32_t rank,
+                                       uint32_t spinLimit, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -58,7 +58,11 @@ class SpmvParams(ctypes.Structure):
     _fields_ = [("rows", c_uint32), ("cols", c_uint32), ("nnz", c_uint32), ("indexBase", c_uint32),
                 ("colIndStride", c_int64), ("valuesStride", c_int64), ("xStride", c_int64), ("yStride", c_int64),
                 ("alpha", c_float), ("beta", c_float), ("alphaPtr", c_void_p), ("betaPtr", c_void_p),
-                ("numMirrors", c_uint32), ("mirrorMulticast", c_uint32), ("mirrorDelta", c_int64 * 7)]
+                ("numMirrors", c_uint32), ("mirrorMulticast", c_uint32), ("mirrorDelta", c_int64 * 7),
+                ("maxRowLenHint", c_uint32)]
+
+
+MAX_ROW_LEN_UNKNOWN = 0xFFFFFFFF  # SpmvParams.maxRowLenHint when the host does not know the longest row
 
 
 class SpmmParams(ctypes.Structure):
@@ -134,6 +138,8 @@ SIGNATURES = {
     "aclsparseB200DnMatSetMirrors": [_P, c_int, POINTER(c_void_p)],
     "aclsparseB200DnVecSetMulticastMirror": [_P, _P],
     "aclsparseB200DnMatSetMulticastMirror": [_P, _P],
+    "aclsparseB200NodeBarrier": [_P, _P, POINTER(c_void_p), c_int, c_int, c_uint32],
+    "aclsparseB200NodeBarrierStatus": [_P, _P, POINTER(c_int)],
     # include/aclsparse_b200_kernels.h
     "spmv_b200_preprocess_kernel_do": [_P, _P, c_uint32, c_uint32, c_uint32, c_int32, c_int64, _P],
     "spmv_b200_kernel_do": [_P, _P, _P, _P, _P, POINTER(SpmvParams), _P],
@@ -141,9 +147,11 @@ SIGNATURES = {
     "spmm_b200_kernel_do": [_P, _P, _P, _P, _P, POINTER(SpmmParams), _P],
     "aclsp_b200_row_block_bounds_kernel_do": [_P, c_uint32, c_uint32, c_int32, c_uint32, _P, _P],
     "aclsp_b200_push_slice_kernel_do": [_P, POINTER(c_void_p), c_uint32, c_int64, c_int64, _P],
+    "aclsp_b200_node_barrier_kernel_do": [_P, POINTER(c_void_p), c_uint32, c_uint32, c_uint32, _P],
 }
 _VOID = {"spmv_b200_preprocess_kernel_do", "spmv_b200_kernel_do", "spmm_b200_preprocess_kernel_do",
-         "spmm_b200_kernel_do", "aclsp_b200_row_block_bounds_kernel_do", "aclsp_b200_push_slice_kernel_do"}
+         "spmm_b200_kernel_do", "aclsp_b200_row_block_bounds_kernel_do", "aclsp_b200_push_slice_kernel_do",
+         "aclsp_b200_node_barrier_kernel_do"}
 
 _lib = None
 

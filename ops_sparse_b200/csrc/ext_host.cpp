@@ -94,3 +94,54 @@ extern "C" aclsparseStatus_t aclsparseB200DnMatSetMirrors(aclsparseDnMatDescr_t 
 {
     return SetMirrors(mat, kDnMatSignature, count, mirrors);
 }
+
+extern "C" aclsparseStatus_t aclsparseB200NodeBarrier(aclrtStream stream, void* localState, void* const* peerStates,
+                                                      int world, int rank, unsigned spinLimit)
+{
+    if (localState == nullptr || peerStates == nullptr || world < 1 || world > ACLSP_BARRIER_MAX_RANKS || rank < 0 ||
+        rank >= world) {
+        return ACL_SPARSE_STATUS_INVALID_VALUE;
+    }
+    for (int r = 0; r < world; ++r) {
+        if (r != rank && peerStates[r] == nullptr) {
+            return ACL_SPARSE_STATUS_INVALID_VALUE;
+        }
+    }
+    if (world == 1) {
+        return ACL_SPARSE_STATUS_SUCCESS;
+    }
+    // About a second: a poll is a system-scope load plus a 64 ns sleep.
+    const unsigned limit = spinLimit != 0 ? spinLimit : 4000000u;
+    (void)cudaGetLastError();
+    aclsp_b200_node_barrier_kernel_do(localState, peerStates, static_cast<uint32_t>(world),
+                                      static_cast<uint32_t>(rank), limit, stream);
+    if (cudaPeekAtLastError() != cudaSuccess) {
+        ACLSP_LOGE("aclsparseB200NodeBarrier", "kernel enqueue failed");
+        return ACL_SPARSE_STATUS_EXECUTION_FAILED;
+    }
+    return ACL_SPARSE_STATUS_SUCCESS;
+}
+
+extern "C" aclsparseStatus_t aclsparseB200NodeBarrierStatus(aclrtStream stream, void* localState, int* missingRank)
+{
+    if (localState == nullptr) {
+        return ACL_SPARSE_STATUS_INVALID_VALUE;
+    }
+    auto s = static_cast<cudaStream_t>(stream);
+    auto* state = static_cast<AclspNodeBarrierState*>(localState);
+    uint32_t status = 0;
+    if (cudaMemcpyAsync(&status, &state->status, sizeof(status), cudaMemcpyDeviceToHost, s) != cudaSuccess ||
+        cudaStreamSynchronize(s) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return ACL_SPARSE_STATUS_EXECUTION_FAILED;
+    }
+    if (status == 0) {
+        return ACL_SPARSE_STATUS_SUCCESS;
+    }
+    if (missingRank != nullptr) {
+        *missingRank = static_cast<int>(status) - 1;
+    }
+    (void)cudaMemsetAsync(&state->status, 0, sizeof(status), s);
+    ACLSP_LOGE("aclsparseB200NodeBarrier", "rank %d did not arrive within the limit", static_cast<int>(status) - 1);
+    return ACL_SPARSE_STATUS_EXECUTION_FAILED;
+}

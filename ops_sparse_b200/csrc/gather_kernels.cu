@@ -5,8 +5,20 @@
  * it writes that block into the result buffer of every other rank through
  * peer-mapped pointers (plain 128-bit stores over NVLink / NVSwitch): one
  * launch, all peers at once, no staging copy and no collective library call.
- * Ranks then meet at a barrier of the caller's choosing.  No TMA, no multicast
- * load: every access to a peer's memory here is an ordinary store.
+ * Ranks then meet at the node barrier below.  No TMA, no multicast load: every
+ * access to a peer's memory here is an ordinary store.
+ *
+ * Node barrier.  Every rank keeps an AclspNodeBarrierState in peer-mapped
+ * memory.  A barrier is one tiny kernel per rank: it counts the rank's epoch
+ * up, stores the epoch into its own slot of every peer's flag array
+ * (st.release.sys, after a system-wide fence, so that the row blocks stored by
+ * the kernels before it are visible first), then polls its own flag array
+ * until every peer has announced the same epoch (ld.acquire.sys).  The poll is
+ * bounded: when a peer does not show up within the limit the kernel sets the
+ * state's status word and returns, the host reads it
+ * (aclsparseB200NodeBarrierStatus) and reports ACL_SPARSE_STATUS_EXECUTION_FAILED.
+ * Nothing traps and nothing spins without a limit, so a rank that is gone
+ * costs its peers the limit, not the GPU.
  *
  * The reference library is single-device; this file has no counterpart there.
  */
@@ -52,7 +64,66 @@ __global__ void PushSliceKernel(const float* __restrict__ src, PeerList peers, i
     }
 }
 
+struct BarrierPeers {
+    AclspNodeBarrierState* ptr[ACLSP_BARRIER_MAX_RANKS];
+};
+
+__device__ __forceinline__ void StoreReleaseSys(uint32_t* addr, uint32_t v)
+{
+    asm volatile("st.release.sys.global.u32 [%0], %1;\n" ::"l"(addr), "r"(v) : "memory");
+}
+
+__device__ __forceinline__ uint32_t LoadAcquireSys(const uint32_t* addr)
+{
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(v) : "l"(addr) : "memory");
+    return v;
+}
+
+// One warp; lane r talks to rank r.
+__global__ void NodeBarrierKernel(AclspNodeBarrierState* local, BarrierPeers peers, uint32_t world, uint32_t rank,
+                                  uint32_t spinLimit)
+{
+    const uint32_t lane = threadIdx.x;
+    uint32_t epoch = 0;
+    if (lane == 0) {
+        epoch = local->epoch + 1u;
+        local->epoch = epoch;
+    }
+    epoch = __shfl_sync(0xffffffffu, epoch, 0);
+    __threadfence_system();  // the stores of the kernels before this one, to any GPU, come first
+    const bool peer = lane < world && lane != rank;
+    if (peer) {
+        StoreReleaseSys(&peers.ptr[lane]->flag[rank], epoch);
+    }
+    bool arrived = !peer;
+    for (uint32_t spin = 0; spin < spinLimit && !arrived; ++spin) {
+        // Epochs only grow; the difference is compared so that a wrapped counter still orders.
+        arrived = static_cast<int32_t>(LoadAcquireSys(&local->flag[lane]) - epoch) >= 0;
+        if (!arrived) {
+            __nanosleep(64);
+        }
+    }
+    if (!arrived) {
+        atomicExch(&local->status, 1u + lane);  // which peer was missing (the last one to report wins)
+    }
+}
+
 }  // namespace
+
+extern "C" void aclsp_b200_node_barrier_kernel_do(void* localState, void* const* peerStates, uint32_t world,
+                                                  uint32_t rank, uint32_t spinLimit, void* stream)
+{
+    if (world <= 1 || world > ACLSP_BARRIER_MAX_RANKS || rank >= world) {
+        return;
+    }
+    BarrierPeers peers{};
+    for (uint32_t r = 0; r < world; ++r) {
+        peers.ptr[r] = static_cast<AclspNodeBarrierState*>(peerStates[r]);
+    }
+    NodeBarrierKernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<AclspNodeBarrierState*>(localState), peers, world, rank, spinLimit);
+}
 
 extern "C" void aclsp_b200_push_slice_kernel_do(const void* src, void* const* peers, uint32_t numPeers,
                                                 int64_t offsetElems, int64_t countElems, void* stream)

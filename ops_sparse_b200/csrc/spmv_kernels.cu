@@ -867,9 +867,11 @@ SpmvRowBlockKernel(const int32_t* __restrict__ colInd, const float* __restrict__
 /* ----------------------------------------------------- carry fix-up -- */
 
 // Rows that span tiles.  A warp looks at 32 tiles, one per lane: tile t needs a fix-up when its
-// first row began in an earlier tile and ends in t.  The warp then takes those tiles one by one:
-// the lanes add the carry-outs of the tiles the row crossed (lane-strided, then a shuffle tree: a
-// fixed order), lane 0 adds the head partial and writes the row.
+// first row began in an earlier tile and ends in t.  Almost always the row began in tile t - 1:
+// the lane adds that tile's carry-out and its own head partial and writes the row.  Rows that
+// crossed several tiles are then taken one by one by the whole warp: the lanes add the carry-outs
+// of the tiles the row crossed (lane-strided, then a shuffle tree: a fixed order), lane 0 adds the
+// head partial and writes the row.
 __global__ void __launch_bounds__(kThreads)
 SpmvCarryFixupKernel(float* __restrict__ y, SpmvPlanView plan, AclspSpmvParams p, const uint32_t* __restrict__ maxRowLen,
                      uint32_t rowBlockCap)
@@ -882,7 +884,15 @@ SpmvCarryFixupKernel(float* __restrict__ y, SpmvPlanView plan, AclspSpmvParams p
     const uint32_t t = warp * 32u + lane;
     const int nnz = static_cast<int>(p.nnz);
     const int64_t total = static_cast<int64_t>(p.rows) + nnz;
-    bool needs = false;
+    const Scalars sc = LoadScalars(p);
+    auto writeRow = [&](int row, double sum) {
+        float* at = y + static_cast<int64_t>(row) * p.yStride;
+        const float out = StoreRow(at, 0, sum, sc);
+        if (p.numMirrors != 0) {
+            MirrorStore(at, out, p);
+        }
+    };
+    bool longRow = false;
     int i0 = 0;
     if (t < plan.numTiles) {
         i0 = plan.tileRow[t];
@@ -890,11 +900,16 @@ SpmvCarryFixupKernel(float* __restrict__ y, SpmvPlanView plan, AclspSpmvParams p
         if (i1 > i0 && i0 >= 0 && i0 < static_cast<int>(p.rows)) {
             int64_t d0 = static_cast<int64_t>(t) * kTile;
             d0 = d0 < total ? d0 : total;
-            needs = ClampOffset(plan.rowPtr[i0], nnz) < d0 - i0;
+            if (ClampOffset(plan.rowPtr[i0], nnz) < d0 - i0) {
+                // t > 0 here: tile 0 starts at item 0, before which no row can begin.
+                longRow = t >= 2 && plan.tileRow[t - 1] == i0;
+                if (!longRow) {
+                    writeRow(i0, plan.carry[2 * (t - 1)] + plan.carry[2 * t + 1]);
+                }
+            }
         }
     }
-    uint32_t todo = __ballot_sync(0xffffffffu, needs);
-    const Scalars sc = LoadScalars(p);
+    uint32_t todo = __ballot_sync(0xffffffffu, longRow);
     while (todo != 0) {
         const int src = __ffs(todo) - 1;
         todo &= todo - 1;
@@ -921,12 +936,7 @@ SpmvCarryFixupKernel(float* __restrict__ y, SpmvPlanView plan, AclspSpmvParams p
             sum += __shfl_xor_sync(0xffffffffu, sum, o);
         }
         if (lane == 0) {
-            sum += plan.carry[2 * tt + 1];
-            float* at = y + static_cast<int64_t>(row) * p.yStride;
-            const float out = StoreRow(at, 0, sum, sc);
-            if (p.numMirrors != 0) {
-                MirrorStore(at, out, p);
-            }
+            writeRow(row, sum + plan.carry[2 * tt + 1]);
         }
     }
 }

@@ -19,8 +19,10 @@ is the reassembly of y / C on every rank, in one of four ways:
   every rank maps, and the peers' buffers are registered as mirrors of the local
   output (``aclsparseB200DnVecSetMirrors`` / ``DnMatSetMirrors``): the product
   kernels store each finished row into all ranks' buffers themselves, over
-  NVLink, while the rest of the matrix is still being multiplied.  A device-side
-  barrier closes the step.  No padding, no concatenation, no separate transfer.
+  NVLink, while the rest of the matrix is still being multiplied.  The library's
+  node barrier (``aclsparseB200NodeBarrier``: one small kernel whose waits are
+  bounded and report through a status word) closes the step.  No padding, no
+  concatenation, no separate transfer.
 * ``push``: same buffers, but the product writes its row block locally and one
   further kernel (``aclsp_b200_push_slice_kernel_do``) stores the block into all
   peers' buffers before the barrier.
@@ -109,14 +111,35 @@ class _PushGather:
         mc = int(getattr(self.handle, "multicast_ptr", 0) or 0) if multicast else 0
         self.multicast_ptr = mc + self.offset * 4 if mc else 0
         self._lib = L.lib()
+        # State of the library's own node barrier (AclspNodeBarrierState: 128 bytes per rank, zero-filled,
+        # addressable by every rank).  Its waits are bounded and report through a status word.
+        self.barrier_state = symm.empty((32,), dtype=torch.int32, device=device)
+        self.barrier_state.zero_()
+        state_handle = symm.rendezvous(self.barrier_state, group=group)
+        self.barrier_peers = (ctypes.c_void_p * self.world)(*[int(p) for p in state_handle.buffer_ptrs])
+        torch.cuda.synchronize()
+        dist.barrier(group=group)  # every state is zero before any rank announces an epoch
 
     def run(self) -> torch.Tensor:
         if not self.fused:
             stream = torch.cuda.current_stream().cuda_stream or 0x1
             self._lib.aclsp_b200_push_slice_kernel_do(self.full.data_ptr(), self.peers, self.num_peers, self.offset,
                                                       self.count, stream)
-        self.handle.barrier()
+        stream = torch.cuda.current_stream().cuda_stream or 0x1
+        status = self._lib.aclsparseB200NodeBarrier(stream, self.barrier_state.data_ptr(), self.barrier_peers,
+                                                    self.world, self.rank, 0)
+        if status != L.SUCCESS:
+            raise RuntimeError(f"aclsparseB200NodeBarrier returned {status}")
         return self.full
+
+    def check_barriers(self) -> None:
+        """Synchronises and raises if a barrier since the last call gave up waiting for a rank."""
+        missing = ctypes.c_int(-1)
+        stream = torch.cuda.current_stream().cuda_stream or 0x1
+        status = self._lib.aclsparseB200NodeBarrierStatus(stream, self.barrier_state.data_ptr(), ctypes.byref(missing))
+        if status != L.SUCCESS:
+            raise RuntimeError(f"node barrier: rank {missing.value} did not arrive within the limit "
+                               f"(status {L.STATUS_NAMES.get(status, status)})")
 
 
 def _make_gather(mode: str, bounds, rank, width, device, group):
@@ -164,7 +187,12 @@ class _GraphedStep:
         self.handle.set_stream(side.cuda_stream)
         try:
             with torch.cuda.stream(side):
-                body()  # first use on this stream: nothing lazy is left for the capture
+                # A plan belongs to the stream it was built on: preprocess again on this one, so that the
+                # captured step holds the product kernels only, then run once eagerly so that nothing
+                # lazy (and no unanswered question about the matrix) is left for the capture.
+                if self.r1 > self.r0:
+                    self.op.preprocess(1.0, 0.0)
+                body()
             side.synchronize()
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, stream=side):

@@ -99,3 +99,44 @@ def test_mirror_list_is_validated():
     with pytest.raises(api.AclsparseError):
         y.set_mirrors([0])      # null mirror
     y.set_mirrors([])           # clears
+
+
+def test_node_barrier_announces_waits_and_gives_up_within_its_limit():
+    """The node barrier on one GPU.  The "peers" are further state blocks of the same device whose flags the
+    test sets by hand, so no kernel ever waits for another kernel: (1) peers that have arrived let the barrier
+    through and receive this rank's epoch; (2) a peer that never arrives makes the barrier give up after its
+    poll limit, the status call reports EXECUTION_FAILED and names the rank, nothing hangs; (3) the next
+    barrier, with every peer present, succeeds again."""
+    lib = L.lib()
+    world, rank = 4, 1
+    states = [torch.zeros(32, dtype=torch.int32, device="cuda") for _ in range(world)]  # epoch, status, -, -, flag[16]
+    ptrs = (ctypes.c_void_p * world)(*[s.data_ptr() for s in states])
+    local = states[rank]
+    missing = ctypes.c_int(-1)
+
+    def arrive(epoch, ranks):
+        for r in ranks:
+            local[4 + r] = epoch
+        torch.cuda.synchronize()
+
+    # (1) everyone is there
+    arrive(1, [0, 2, 3])
+    assert lib.aclsparseB200NodeBarrier(0x1, local.data_ptr(), ptrs, world, rank, 1000) == L.SUCCESS
+    assert lib.aclsparseB200NodeBarrierStatus(0x1, local.data_ptr(), ctypes.byref(missing)) == L.SUCCESS
+    for r in (0, 2, 3):
+        assert int(states[r][4 + rank]) == 1          # announced to every peer
+    assert int(local[0]) == 1
+    # (2) rank 2 never announces epoch 2: the wait runs out after 2000 polls (well under a second)
+    arrive(2, [0, 3])
+    assert lib.aclsparseB200NodeBarrier(0x1, local.data_ptr(), ptrs, world, rank, 2000) == L.SUCCESS  # enqueue
+    st = lib.aclsparseB200NodeBarrierStatus(0x1, local.data_ptr(), ctypes.byref(missing))
+    assert st == L.EXECUTION_FAILED and missing.value == 2
+    assert int(states[0][4 + rank]) == 2              # it did announce itself before giving up
+    # (3) the record was cleared; with every peer present the next barrier is fine
+    arrive(3, [0, 2, 3])
+    assert lib.aclsparseB200NodeBarrier(0x1, local.data_ptr(), ptrs, world, rank, 2000) == L.SUCCESS
+    assert lib.aclsparseB200NodeBarrierStatus(0x1, local.data_ptr(), ctypes.byref(missing)) == L.SUCCESS
+    # argument checks never reach the device
+    assert lib.aclsparseB200NodeBarrier(0x1, None, ptrs, world, rank, 0) == L.INVALID_VALUE
+    assert lib.aclsparseB200NodeBarrier(0x1, local.data_ptr(), ptrs, 17, rank, 0) == L.INVALID_VALUE
+    assert lib.aclsparseB200NodeBarrier(0x1, local.data_ptr(), ptrs, world, 4, 0) == L.INVALID_VALUE
