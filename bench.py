@@ -240,25 +240,99 @@ class Context:
         return float(t.item())
 
 
+def shared_dir(ctx: Context) -> str:
+    """Scratch directory in shared memory that the ranks of this run exchange host arrays through."""
+    return os.path.join("/dev/shm", f"aclsp_bench_{os.environ.get('MASTER_PORT', '0')}_{os.getuid()}")
+
+
+def make_workload(ctx: Context, name: str, rows) -> dict:
+    """The configuration's host arrays: generated once (rank 0) and mapped by the other ranks, so that N ranks do
+    not spend N times the generation time and memory."""
+    if ctx.world == 1:
+        return workloads.make(name, rows=rows)
+    base = os.path.join(shared_dir(ctx), f"cfg_{name}")
+    if ctx.rank == 0:
+        cfg = workloads.make(name, rows=rows)
+        os.makedirs(base, exist_ok=True)
+        scalars = {}
+        for key, value in cfg.items():
+            if isinstance(value, np.ndarray):
+                np.save(os.path.join(base, key + ".npy"), value)
+            else:
+                scalars[key] = value
+        with open(os.path.join(base, "scalars.json"), "w") as f:
+            json.dump(scalars, f)
+    ctx.barrier()
+    if ctx.rank != 0:
+        with open(os.path.join(base, "scalars.json")) as f:
+            cfg = json.load(f)
+        for fname in os.listdir(base):
+            if fname.endswith(".npy"):
+                cfg[fname[:-4]] = np.asarray(np.load(os.path.join(base, fname), mmap_mode="r"))
+    ctx.barrier()
+    return cfg
+
+
+def cleanup_shared(ctx: Context) -> None:
+    if ctx.world > 1:
+        ctx.barrier()
+        if ctx.rank == 0:
+            import shutil
+            shutil.rmtree(shared_dir(ctx), ignore_errors=True)
+
+
+_truth_serial = [0]
+
+
 def check_whole_result(ctx: Context, cfg: dict, full, alpha: float, beta: float) -> dict:
-    """This rank's whole reassembled y / C against the oracle's fp64 truth; reduced over ranks."""
+    """This rank's whole reassembled y / C against the oracle's fp64 truth; reduced over ranks.  The truth is
+    computed once per check: every rank computes an equal share of the rows with its share of the host threads
+    and the shares are exchanged through shared memory; the comparison covers all rows on every rank."""
     from oracle import oracle as O
     threads = max(1, host_threads() // ctx.world)
     rows = cfg["rows"]
+    spmv = cfg["kind"] == "spmv"
+    n = 1 if spmv else cfg["n"]
+
+    def truth_of(r0, r1):
+        if spmv:
+            sub_ptr = np.ascontiguousarray(cfg["row_ptr"][r0:r1 + 1])
+            p0, p1 = int(sub_ptr[0]), int(sub_ptr[-1])
+            return O.spmv_f64(sub_ptr - p0, cfg["col_ind"][p0:p1], cfg["values"][p0:p1], cfg["x"], cfg["y"][r0:r1],
+                              alpha, beta, threads=threads)
+        return O.spmm_f64(cfg["row_ptr"], cfg["col_ind"], cfg["values"], cfg["b"], n, cfg["c"], n, n, cfg["cols"],
+                          alpha, beta, row_begin=r0, row_end=r1, threads=threads)
+
     bad, max_abs, max_rel = 0, 0.0, 0.0
-    if cfg["kind"] == "spmv":
-        truth = O.spmv_f64(cfg["row_ptr"], cfg["col_ind"], cfg["values"], cfg["x"], cfg["y"], alpha, beta,
-                           threads=threads)
-        bad, max_abs, max_rel = O.check_tolerance(full[:rows].cpu().numpy(), truth)
-    else:
-        n = cfg["n"]
-        chunk = max(1, (1 << 27) // n)  # a GiB of fp64 truth at a time
+    chunk = max(1, (1 << 27) // n)  # a GiB of fp64 truth at a time
+    if ctx.world == 1:
         for r0 in range(0, rows, chunk):
             r1 = min(rows, r0 + chunk)
-            truth = O.spmm_f64(cfg["row_ptr"], cfg["col_ind"], cfg["values"], cfg["b"], n, cfg["c"], n, n,
-                               cfg["cols"], alpha, beta, row_begin=r0, row_end=r1, threads=threads)
-            b, a, r = O.check_tolerance(full[r0:r1].cpu().numpy(), truth)
+            b, a, r = O.check_tolerance(full[r0:r1].cpu().numpy(), truth_of(r0, r1))
             bad, max_abs, max_rel = bad + b, max(max_abs, a), max(max_rel, r)
+    else:
+        _truth_serial[0] += 1
+        base = os.path.join(shared_dir(ctx), f"truth_{cfg['name']}_{_truth_serial[0]}")
+        share = (rows + ctx.world - 1) // ctx.world
+        lo, hi = min(ctx.rank * share, rows), min((ctx.rank + 1) * share, rows)
+        if ctx.rank == 0:
+            os.makedirs(base, exist_ok=True)
+        ctx.barrier()
+        np.save(os.path.join(base, f"{ctx.rank}.npy"), truth_of(lo, hi) if hi > lo else np.empty((0,) + (() if spmv else (n,))))
+        ctx.barrier()
+        for g in range(ctx.world):
+            g0, g1 = min(g * share, rows), min((g + 1) * share, rows)
+            if g1 <= g0:
+                continue
+            truth = np.load(os.path.join(base, f"{g}.npy"), mmap_mode="r")
+            for r0 in range(g0, g1, chunk):
+                r1 = min(g1, r0 + chunk)
+                b, a, r = O.check_tolerance(full[r0:r1].cpu().numpy(), np.asarray(truth[r0 - g0:r1 - g0]))
+                bad, max_abs, max_rel = bad + b, max(max_abs, a), max(max_rel, r)
+        ctx.barrier()
+        if ctx.rank == 0:
+            import shutil
+            shutil.rmtree(base, ignore_errors=True)
     return {"rows_checked": rows, "violations": int(ctx.max_over_ranks(float(bad))),
             "ranks_checked": int(ctx.sum_over_ranks(1.0)), "max_abs_err": ctx.max_over_ranks(max_abs),
             "max_rel_err": ctx.max_over_ranks(max_rel), "rtol": 1e-5, "atol": 1e-6}
@@ -391,7 +465,7 @@ def measure(ctx: Context, args, cfg: dict, steps: int, warmup: int, min_warm_sec
     achieved = abytes / (k_ms * 1e-3) / 1e9 if k_ms else None
     ratio = TRAFFIC_RATIO.get(cfg["name"])
     traffic = int(abytes * ratio) if ratio and args.rows is None else None
-    launches = op.launches_per_step()
+    launches = op.launches_per_step(alpha, beta)
     result = {
         "metric": metric_name(cfg), "value": flop / (ms_step * 1e-3) / 1e9, "unit": "GFLOP/s",
         "ms_per_step": ms_step, "steps": steps, "warmup": done,
@@ -430,7 +504,7 @@ def run_ours(args):
     sampler = ClockSampler(ctx.device.index or 0)
     if rank == 0:
         sampler.start()
-    cfg = workloads.make(args.workload, rows=args.rows)
+    cfg = make_workload(ctx, args.workload, args.rows)
     head = measure(ctx, args, cfg, args.steps, args.warmup, 1.5)
     clocks = sampler.stop() if rank == 0 else None
 
@@ -452,12 +526,13 @@ def run_ours(args):
     for name in names:
         if name == args.workload and args.rows is None:
             continue
-        other = workloads.make(name, rows=args.rows if args.rows is not None and name != "c1" else None)
+        other = make_workload(ctx, name, args.rows if args.rows is not None and name != "c1" else None)
         steps = args.steps if other["kind"] == "spmv" else max(3, min(args.steps, 10))
         configs[name] = measure(ctx, args, other, steps, max(3, args.warmup), 0.25)
         del other
         gc.collect()
 
+    cleanup_shared(ctx)
     if world > 1:
         ctx.dist.barrier()  # last collective: every rank reaches it before any rank leaves
     if rank != 0:

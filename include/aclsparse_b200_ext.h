@@ -13,6 +13,11 @@
 extern "C" {
 #endif
 
+/* The library is built with hidden visibility: only what this header declares is exported. */
+#if defined(__GNUC__)
+#pragma GCC visibility push(default)
+#endif
+
 /* Row-block boundaries that balance the non-zeros of a CSR matrix over `parts`
  * devices.  Writes parts+1 int32 values to the DEVICE array `bounds`
  * (asynchronously, on the handle's stream):
@@ -31,7 +36,9 @@ aclsparseStatus_t aclsparseB200RowBlockBounds(aclsparseHandle_t handle, aclspars
  * is only handed its operands.  Asynchronous on `stream`.
  *   - Matrices whose plan exceeds the built-in scratch (roughly rows * 4 + (rows + nnz) * 0.012 bytes
  *     > 8 MiB) are refused with ACL_SPARSE_STATUS_INSUFFICIENT_RESOURCES and a message on stderr.
- *   - The first call on a device looks up the scratch's device address; make it outside stream capture.
+ *   - The first call on a device loads the library's device code (with it the scratch array) and looks up
+ *     the scratch's device address: that call can take device memory once and must be made at start-up,
+ *     outside any stream capture.  Every later call on that device allocates nothing.
  *   - All calls on a device share the scratch: calls that overlap on the GPU race; keep them in stream order.
  * This entry point has no counterpart in the reference. */
 aclsparseStatus_t aclsparseB200SpMVNoAlloc(aclrtStream stream, int64_t rows, int64_t cols, int64_t nnz,
@@ -71,6 +78,10 @@ aclsparseStatus_t aclsparseB200DnMatSetMulticastMirror(aclsparseDnMatDescr_t mat
 aclsparseStatus_t aclsparseB200NodeBarrier(aclrtStream stream, void* localState, void* const* peerStates, int world,
                                            int rank, unsigned spinLimit);
 aclsparseStatus_t aclsparseB200NodeBarrierStatus(aclrtStream stream, void* localState, int* missingRank);
+
+#if defined(__GNUC__)
+#pragma GCC visibility pop
+#endif
 
 #ifdef __cplusplus
 }

@@ -19,6 +19,11 @@
 extern "C" {
 #endif
 
+/* The library is built with hidden visibility: only what this header declares is exported. */
+#if defined(__GNUC__)
+#pragma GCC visibility push(default)
+#endif
+
 /* Mirrors of an output: besides the result buffer itself a kernel can store every element it writes at the
  * same element position of up to ACLSP_MAX_MIRRORS further buffers - the result buffers of the other GPUs
  * of the node, mapped into this device's address space - so that the product and the reassembly of the
@@ -53,6 +58,10 @@ typedef struct AclspSpmvParams {
      * has learnt it (an asynchronous copy to pinned memory), else ACLSP_MAX_ROW_LEN_UNKNOWN: then both
      * SpMV kernels are launched and decide by the plan header which of them computes. */
     uint32_t maxRowLenHint;
+    /* The vector that beta scales when it is not y itself (Z = alpha*A*X + beta*Y, the SpMVOp form):
+     * element i at betaSource[i * betaSourceStride].  NULL: y is updated in place. */
+    const float* betaSource;
+    int64_t betaSourceStride;
 } AclspSpmvParams;
 
 #define ACLSP_MAX_ROW_LEN_UNKNOWN 0xFFFFFFFFu
@@ -113,11 +122,36 @@ void aclsp_b200_row_block_bounds_kernel_do(const void* rowPtr, uint32_t rows, ui
                                            uint32_t parts, void* bounds, void* stream);
 
 /* Copies `countElems` floats at element `offsetElems` of `src` to the same place in each of the
- * `numPeers` (at most 16) buffers of the host array `peers` - peer-mapped device pointers of the other
+ * `numPeers` buffers (16 per launch; a peer buffer aligned differently from `src` gets 4-byte stores) of the host array `peers` - peer-mapped device pointers of the other
  * ranks' result buffers - with plain stores, all peers in one launch.  The caller supplies the barrier
  * that follows.  No counterpart in the reference, which is single-device. */
 void aclsp_b200_push_slice_kernel_do(const void* src, void* const* peers, uint32_t numPeers, int64_t offsetElems,
                                      int64_t countElems, void* stream);
+
+/* op(A) = transpose.  Builds the transpose of the CSR matrix in `workspace` as a CSR matrix of its own:
+ * row offsets at the place where a plan keeps them (so that the preprocess launcher above can then be run
+ * on them in place), column indices (the original row numbers, ascending inside a row), and the
+ * permutation perm[p] = original index of transposed entry p; entries of one column keep their original
+ * order (a stable counting sort), so the result does not depend on scheduling.  `layout` is a host
+ * pointer to the offsets (AclspTransposeLayout, csrc/plan_layout.h).  Replaces the reference's host-built
+ * CSC copy (sparse/spmm/arch35/host/spmm_csr_mat.cpp:212-315) and stands in for its transposed SpMV
+ * kernels (sparse/spmv/arch35/spmv_kernel.cpp:579-879). */
+struct AclspTransposeLayout;
+void aclsp_b200_transpose_build_kernel_do(const void* rowPtr, const void* colInd, uint32_t rows, uint32_t cols,
+                                          uint32_t nnz, int32_t indexBase, int64_t rowPtrStride,
+                                          int64_t colIndStride, void* workspace,
+                                          const struct AclspTransposeLayout* layout, void* stream);
+
+/* valuesT[p] = values[perm[p] * valuesStride] into the workspace of a transpose built by the call above
+ * (the per-product part of op(A) = transpose).  Replaces spmm_transpose_values_launch
+ * (reference: sparse/spmm/arch35/kernel/spmm_kernel_transpose.cpp:62). */
+void aclsp_b200_transpose_values_kernel_do(const void* values, int64_t valuesStride, uint32_t cols, uint32_t nnz,
+                                           void* workspace, const struct AclspTransposeLayout* layout,
+                                           void* stream);
+
+/* Number of kernels this library has launched in this process so far (all entry points, all streams;
+ * launches recorded into a CUDA graph count once, at capture).  A diagnostic for benchmarks. */
+uint64_t aclsp_b200_kernel_launches(void);
 
 /* State of the node barrier, one per rank, in memory that every rank of the node can address (peer-mapped /
  * symmetric memory), zero-filled before the first barrier.  epoch: barriers this rank has entered.
@@ -138,6 +172,10 @@ typedef struct AclspNodeBarrierState {
  * `rank` is unused).  One warp, one launch.  No counterpart in the reference, which is single-device. */
 void aclsp_b200_node_barrier_kernel_do(void* localState, void* const* peerStates, uint32_t world, uint32_t rank,
                                        uint32_t spinLimit, void* stream);
+
+#if defined(__GNUC__)
+#pragma GCC visibility pop
+#endif
 
 #ifdef __cplusplus
 }

@@ -26,6 +26,11 @@
 extern "C" {
 #endif
 
+/* The library is built with hidden visibility: only what this header declares is exported. */
+#if defined(__GNUC__)
+#pragma GCC visibility push(default)
+#endif
+
 /* ---------------------------------------------------------------- enums -- */
 
 /* reference: include/cann_ops_sparse.h:32-36 */
@@ -313,6 +318,102 @@ aclsparseStatus_t aclsparseSpMM(aclsparseHandle_t handle, aclsparseOperation_t o
                                 const void* alpha, aclsparseConstSpMatDescr_t matA, aclsparseConstDnMatDescr_t matB,
                                 const void* beta, aclsparseDnMatDescr_t matC, aclDataType computeType,
                                 aclsparseSpMMAlg_t alg, void* buffer);
+
+/* ------------------------------------------------------- SpMVOp / SpMMOp -- */
+
+/* The plan API: create once, execute many.
+ *   bufferSize -> createDescr (binds A, preprocesses into `buffer`) -> createPlan
+ *   -> [setGlobalUserData] -> execute (repeatable) -> destroyPlan -> destroyDescr
+ * SpMVOp: Z = alpha*A*X + beta*Y with Z a vector of its own (Z may be Y).  SpMMOp: C = alpha*A*op(B) +
+ * beta*C, B and C given at execute.  op(A) is NON_TRANSPOSE, data fp32, indices int32.  Every algorithm
+ * value needs the buffer, adds in a fixed order (results are bit-wise reproducible) and picks up new
+ * values of A at the next execute.  `buffer` stays the caller's and must outlive the descriptor. */
+
+/* reference: include/cann_ops_sparse.h:69-83 */
+typedef enum aclsparseSpMVOpAlg_t {
+    ACL_SPARSE_SPMVOP_ALG_DEFAULT = 0,
+    ACL_SPARSE_SPMVOP_ALG1,
+    ACL_SPARSE_SPMVOP_ALG2
+} aclsparseSpMVOpAlg_t;
+
+/* reference: include/cann_ops_sparse.h:2412-2417 */
+typedef enum aclsparseSpMMOpAlg_t {
+    ACL_SPARSE_SPMMOP_ALG_DEFAULT = 0,
+    ACL_SPARSE_SPMMOP_ALG1,
+    ACL_SPARSE_SPMMOP_ALG2,
+    ACL_SPARSE_SPMMOP_ALG1_HIGH_PRECISION
+} aclsparseSpMMOpAlg_t;
+
+/* reference: include/cann_ops_sparse.h:86-91, 2420-2425 */
+struct aclsparseSpMVOpDescr;
+struct aclsparseSpMVOpPlan;
+typedef struct aclsparseSpMVOpDescr* aclsparseSpMVOpDescr_t;
+typedef struct aclsparseSpMVOpDescr const* aclsparseConstSpMVOpDescr_t;
+typedef struct aclsparseSpMVOpPlan* aclsparseSpMVOpPlan_t;
+struct aclsparseSpMMOpDescr;
+struct aclsparseSpMMOpPlan;
+typedef struct aclsparseSpMMOpDescr* aclsparseSpMMOpDescr_t;
+typedef struct aclsparseSpMMOpDescr const* aclsparseConstSpMMOpDescr_t;
+typedef struct aclsparseSpMMOpPlan* aclsparseSpMMOpPlan_t;
+
+/* reference: include/cann_ops_sparse.h:2345 (sparse/spmv_op/arch35/spmv_op_host.cpp:520-559) */
+aclsparseStatus_t aclsparseSpMVOp_bufferSize(aclsparseHandle_t handle, aclsparseOperation_t opA,
+                                             aclsparseConstSpMatDescr_t matA, aclsparseConstDnVecDescr_t vecX,
+                                             aclsparseConstDnVecDescr_t vecY, aclsparseDnVecDescr_t vecZ,
+                                             aclDataType computeType, aclsparseSpMVOpAlg_t alg, size_t* bufferSize);
+/* reference: include/cann_ops_sparse.h:2355 (spmv_op_host.cpp:630-673) */
+aclsparseStatus_t aclsparseSpMVOp_createDescr(aclsparseHandle_t handle, aclsparseSpMVOpDescr_t* descr,
+                                              aclsparseOperation_t opA, aclsparseConstSpMatDescr_t matA,
+                                              aclsparseConstDnVecDescr_t vecX, aclsparseConstDnVecDescr_t vecY,
+                                              aclsparseDnVecDescr_t vecZ, aclDataType computeType,
+                                              aclsparseSpMVOpAlg_t alg, void* buffer);
+/* reference: include/cann_ops_sparse.h:2365 (spmv_op_host.cpp:676-683); NULL is SUCCESS */
+aclsparseStatus_t aclsparseSpMVOp_destroyDescr(aclsparseSpMVOpDescr_t descr);
+/* reference: include/cann_ops_sparse.h:2371 (spmv_op_host.cpp:686-712); the epilogue buffer must be NULL */
+aclsparseStatus_t aclsparseSpMVOp_createPlan(aclsparseHandle_t handle, aclsparseSpMVOpDescr_t descr,
+                                             aclsparseSpMVOpPlan_t* plan, const void* epilogueLTOBuffer,
+                                             size_t epilogueLTOBufferSize);
+/* reference: include/cann_ops_sparse.h:2380 (spmv_op_host.cpp:715-722); NULL is SUCCESS */
+aclsparseStatus_t aclsparseSpMVOp_destroyPlan(aclsparseSpMVOpPlan_t plan);
+/* reference: include/cann_ops_sparse.h:2386 (spmv_op_host.cpp:725-749); identity epilogue: nothing to set */
+aclsparseStatus_t aclsparseSpMVOp_setGlobalUserData(aclsparseHandle_t handle, aclsparseSpMVOpPlan_t plan,
+                                                    const char* epilogueDataName, void* epilogueData,
+                                                    size_t epilogueDataSize);
+/* reference: include/cann_ops_sparse.h:2394 (spmv_op_host.cpp:752-772) */
+aclsparseStatus_t aclsparseSpMVOp(aclsparseHandle_t handle, aclsparseSpMVOpPlan_t plan, const void* alpha,
+                                  const void* beta, aclsparseConstDnVecDescr_t vecX, aclsparseConstDnVecDescr_t vecY,
+                                  aclsparseDnVecDescr_t vecZ);
+
+/* reference: include/cann_ops_sparse.h:2431 (sparse/spmm_op/arch35/spmm_op_host.cpp:695-730) */
+aclsparseStatus_t aclsparseSpMMOp_bufferSize(aclsparseHandle_t handle, aclsparseOperation_t opA,
+                                             aclsparseOperation_t opB, aclsparseConstSpMatDescr_t matA,
+                                             aclsparseConstDnMatDescr_t matB, aclsparseDnMatDescr_t matC,
+                                             aclDataType computeType, aclsparseSpMMOpAlg_t alg, size_t* bufferSize);
+/* reference: include/cann_ops_sparse.h:2442 */
+aclsparseStatus_t aclsparseSpMMOp_createDescr(aclsparseHandle_t handle, aclsparseSpMMOpDescr_t* descr,
+                                              aclsparseOperation_t opA, aclsparseOperation_t opB,
+                                              aclsparseConstSpMatDescr_t matA, aclsparseConstDnMatDescr_t matB,
+                                              aclsparseDnMatDescr_t matC, aclDataType computeType,
+                                              aclsparseSpMMOpAlg_t alg, void* buffer);
+/* reference: include/cann_ops_sparse.h:2452; NULL is SUCCESS */
+aclsparseStatus_t aclsparseSpMMOp_destroyDescr(aclsparseSpMMOpDescr_t descr);
+/* reference: include/cann_ops_sparse.h:2458; the epilogue buffer must be NULL */
+aclsparseStatus_t aclsparseSpMMOp_createPlan(aclsparseHandle_t handle, aclsparseSpMMOpDescr_t descr,
+                                             aclsparseSpMMOpPlan_t* plan, const void* epilogueLTOBuffer,
+                                             size_t epilogueLTOBufferSize);
+/* reference: include/cann_ops_sparse.h:2467; NULL is SUCCESS */
+aclsparseStatus_t aclsparseSpMMOp_destroyPlan(aclsparseSpMMOpPlan_t plan);
+/* reference: include/cann_ops_sparse.h:2473 */
+aclsparseStatus_t aclsparseSpMMOp_setGlobalUserData(aclsparseHandle_t handle, aclsparseSpMMOpPlan_t plan,
+                                                    const char* epilogueDataName, void* epilogueData,
+                                                    size_t epilogueDataSize);
+/* reference: include/cann_ops_sparse.h:2484 */
+aclsparseStatus_t aclsparseSpMMOp(aclsparseHandle_t handle, aclsparseSpMMOpPlan_t plan, const void* alpha,
+                                  const void* beta, aclsparseConstDnMatDescr_t matB, aclsparseDnMatDescr_t matC);
+
+#if defined(__GNUC__)
+#pragma GCC visibility pop
+#endif
 
 #ifdef __cplusplus
 }

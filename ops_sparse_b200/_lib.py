@@ -59,7 +59,7 @@ class SpmvParams(ctypes.Structure):
                 ("colIndStride", c_int64), ("valuesStride", c_int64), ("xStride", c_int64), ("yStride", c_int64),
                 ("alpha", c_float), ("beta", c_float), ("alphaPtr", c_void_p), ("betaPtr", c_void_p),
                 ("numMirrors", c_uint32), ("mirrorMulticast", c_uint32), ("mirrorDelta", c_int64 * 7),
-                ("maxRowLenHint", c_uint32)]
+                ("maxRowLenHint", c_uint32), ("betaSource", c_void_p), ("betaSourceStride", c_int64)]
 
 
 MAX_ROW_LEN_UNKNOWN = 0xFFFFFFFF  # SpmvParams.maxRowLenHint when the host does not know the longest row
@@ -131,6 +131,20 @@ SIGNATURES = {
     "aclsparseSpMMGetBufferSize": [_P, c_int, c_int, _P, _P, _P, _P, _P, c_int, c_int, POINTER(c_size_t)],
     "aclsparseSpMMPreprocess": [_P, c_int, c_int, _P, _P, _P, _P, _P, c_int, c_int, _P],
     "aclsparseSpMM": [_P, c_int, c_int, _P, _P, _P, _P, _P, c_int, c_int, _P],
+    "aclsparseSpMVOp_bufferSize": [_P, c_int, _P, _P, _P, _P, c_int, c_int, POINTER(c_size_t)],
+    "aclsparseSpMVOp_createDescr": [_P, _PP, c_int, _P, _P, _P, _P, c_int, c_int, _P],
+    "aclsparseSpMVOp_destroyDescr": [_P],
+    "aclsparseSpMVOp_createPlan": [_P, _P, _PP, _P, c_size_t],
+    "aclsparseSpMVOp_destroyPlan": [_P],
+    "aclsparseSpMVOp_setGlobalUserData": [_P, _P, ctypes.c_char_p, _P, c_size_t],
+    "aclsparseSpMVOp": [_P, _P, _P, _P, _P, _P, _P],
+    "aclsparseSpMMOp_bufferSize": [_P, c_int, c_int, _P, _P, _P, c_int, c_int, POINTER(c_size_t)],
+    "aclsparseSpMMOp_createDescr": [_P, _PP, c_int, c_int, _P, _P, _P, c_int, c_int, _P],
+    "aclsparseSpMMOp_destroyDescr": [_P],
+    "aclsparseSpMMOp_createPlan": [_P, _P, _PP, _P, c_size_t],
+    "aclsparseSpMMOp_destroyPlan": [_P],
+    "aclsparseSpMMOp_setGlobalUserData": [_P, _P, ctypes.c_char_p, _P, c_size_t],
+    "aclsparseSpMMOp": [_P, _P, _P, _P, _P, _P],
     # include/aclsparse_b200_ext.h
     "aclsparseB200RowBlockBounds": [_P, _P, c_int, _P],
     "aclsparseB200SpMVNoAlloc": [_P, c_int64, c_int64, c_int64, _P, _P, _P, c_int, _P, _P, c_float, c_float],
@@ -148,10 +162,14 @@ SIGNATURES = {
     "aclsp_b200_row_block_bounds_kernel_do": [_P, c_uint32, c_uint32, c_int32, c_uint32, _P, _P],
     "aclsp_b200_push_slice_kernel_do": [_P, POINTER(c_void_p), c_uint32, c_int64, c_int64, _P],
     "aclsp_b200_node_barrier_kernel_do": [_P, POINTER(c_void_p), c_uint32, c_uint32, c_uint32, _P],
+    "aclsp_b200_kernel_launches": [],
+    "aclsp_b200_transpose_build_kernel_do": [_P, _P, c_uint32, c_uint32, c_uint32, c_int32, c_int64, c_int64, _P, _P, _P],
+    "aclsp_b200_transpose_values_kernel_do": [_P, c_int64, c_uint32, c_uint32, _P, _P, _P],
 }
 _VOID = {"spmv_b200_preprocess_kernel_do", "spmv_b200_kernel_do", "spmm_b200_preprocess_kernel_do",
          "spmm_b200_kernel_do", "aclsp_b200_row_block_bounds_kernel_do", "aclsp_b200_push_slice_kernel_do",
-         "aclsp_b200_node_barrier_kernel_do"}
+         "aclsp_b200_node_barrier_kernel_do", "aclsp_b200_transpose_build_kernel_do",
+         "aclsp_b200_transpose_values_kernel_do"}
 
 _lib = None
 
@@ -168,6 +186,6 @@ def lib() -> ctypes.CDLL:
         for name, args in SIGNATURES.items():
             fn = getattr(handle, name)
             fn.argtypes = args
-            fn.restype = None if name in _VOID else c_int
+            fn.restype = None if name in _VOID else (ctypes.c_uint64 if name == "aclsp_b200_kernel_launches" else c_int)
         _lib = handle
     return _lib

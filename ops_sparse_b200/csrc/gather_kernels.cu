@@ -27,6 +27,7 @@
 #include <cuda_runtime.h>
 
 #include "aclsparse_b200_kernels.h"
+#include "plan_kernels.h"
 
 namespace {
 
@@ -42,16 +43,18 @@ __global__ void PushSliceKernel(const float* __restrict__ src, PeerList peers, i
 {
     float* __restrict__ dst = peers.ptr[blockIdx.y] + offset;
     const float* __restrict__ from = src + offset;
-    // Both sides sit at the same offset of equally aligned buffers, so one
-    // prologue brings both to a 16-byte boundary.
+    // Where both sides sit at the same offset of equally aligned buffers, one prologue brings both
+    // to a 16-byte boundary and the body moves 16-byte vectors; a peer buffer aligned differently
+    // from the source gets plain 4-byte stores throughout.
+    const bool sameAlignment = ((reinterpret_cast<uintptr_t>(from) ^ reinterpret_cast<uintptr_t>(dst)) & 15u) == 0;
     const int64_t mis = (reinterpret_cast<uintptr_t>(from) & 15u) / 4u;
     int64_t head = mis == 0 ? 0 : 4 - mis;
-    head = head < count ? head : count;
+    head = sameAlignment ? (head < count ? head : count) : count;
     const int64_t vecs = (count - head) / 4;
     const int64_t tid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     const int64_t step = static_cast<int64_t>(gridDim.x) * blockDim.x;
-    if (tid < head) {
-        dst[tid] = from[tid];
+    for (int64_t i = tid; i < head; i += step) {
+        dst[i] = from[i];
     }
     const float4* from4 = reinterpret_cast<const float4*>(from + head);
     float4* dst4 = reinterpret_cast<float4*>(dst + head);
@@ -121,6 +124,7 @@ extern "C" void aclsp_b200_node_barrier_kernel_do(void* localState, void* const*
     for (uint32_t r = 0; r < world; ++r) {
         peers.ptr[r] = static_cast<AclspNodeBarrierState*>(peerStates[r]);
     }
+    AclspCountLaunches(1);
     NodeBarrierKernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<AclspNodeBarrierState*>(localState), peers, world, rank, spinLimit);
 }
@@ -131,15 +135,20 @@ extern "C" void aclsp_b200_push_slice_kernel_do(const void* src, void* const* pe
     if (numPeers == 0 || countElems <= 0) {
         return;
     }
-    PeerList list{};
-    const uint32_t n = numPeers > kMaxPeers ? kMaxPeers : numPeers;
-    for (uint32_t i = 0; i < n; ++i) {
-        list.ptr[i] = static_cast<float*>(peers[i]);
+    // A launch serves up to kMaxPeers peers; longer lists take further launches.
+    for (uint32_t first = 0; first < numPeers; first += kMaxPeers) {
+        PeerList list{};
+        const uint32_t n = numPeers - first > kMaxPeers ? kMaxPeers : numPeers - first;
+        for (uint32_t i = 0; i < n; ++i) {
+            list.ptr[i] = static_cast<float*>(peers[first + i]);
+        }
+        // Enough blocks to keep the links busy, few enough to launch quickly.
+        int64_t blocks = (countElems / 4 + 255) / 256;
+        blocks = blocks < 1 ? 1
+                            : (blocks > 592 / static_cast<int64_t>(n) + 1 ? 592 / static_cast<int64_t>(n) + 1 : blocks);
+        const dim3 grid(static_cast<unsigned>(blocks), n);
+        AclspCountLaunches(1);
+        PushSliceKernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const float*>(src), list,
+                                                                            offsetElems, countElems);
     }
-    // Enough blocks to keep the links busy, few enough to launch quickly.
-    int64_t blocks = (countElems / 4 + 255) / 256;
-    blocks = blocks < 1 ? 1 : (blocks > 592 / static_cast<int64_t>(n) + 1 ? 592 / static_cast<int64_t>(n) + 1 : blocks);
-    const dim3 grid(static_cast<unsigned>(blocks), n);
-    PushSliceKernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const float*>(src), list,
-                                                                        offsetElems, countElems);
 }

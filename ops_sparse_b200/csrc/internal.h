@@ -85,6 +85,8 @@ struct SpmvPlanRecord {
 // sparse/spmm/arch35/host/spmm_host.cpp:63-97, and pays a host rebuild).
 struct SpmmPlanRecord {
     const void* buffer = nullptr;
+    bool transposed = false;            // the buffer holds the plan of the transpose, and the transpose
+    const void* colIndices = nullptr;   // what that transpose was built from
     const void* rowOffsets = nullptr;
     uint64_t rows = 0;
     uint64_t cols = 0;

@@ -170,9 +170,11 @@ void AclspLaunchPlanBuild(const void* rowPtr, void* workspace, uint32_t rows, ui
     const uint64_t entries = static_cast<uint64_t>(rows) + 1u;
     uint64_t blocks = (entries + 255u) / 256u;
     blocks = blocks > 148u * 16u ? 148u * 16u : blocks;
+    AclspCountLaunches(1);
     NormalizeRowOffsetsKernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
         static_cast<const int32_t*>(rowPtr), dst, rows, indexBase, rowOffsetsStride, longest);
     const uint32_t splitBlocks = (layout.numTiles + 1u + 127u) / 128u;
+    AclspCountLaunches(1);
     TileSplitKernel<<<splitBlocks, 128, 0, stream>>>(workspace, rows, cols, nnz, indexBase, tileItems, kind,
                                                      denseCols, classDiv, layout);
 }
@@ -195,6 +197,7 @@ extern "C" void spmm_b200_preprocess_kernel_do(const void* rowPtr, void* workspa
 extern "C" void aclsp_b200_row_block_bounds_kernel_do(const void* rowPtr, uint32_t rows, uint32_t nnz,
                                                       int32_t indexBase, uint32_t parts, void* bounds, void* stream)
 {
+    AclspCountLaunches(1);
     RowBlockBoundsKernel<<<(parts + 1u + 63u) / 64u, 64, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const int32_t*>(rowPtr), rows, nnz, indexBase, parts, static_cast<int32_t*>(bounds));
 }

@@ -12,4 +12,8 @@ void AclspLaunchPlanBuild(const void* rowPtr, void* workspace, uint32_t rows, ui
                           int32_t indexBase, int64_t rowOffsetsStride, uint32_t kind, uint32_t denseCols,
                           cudaStream_t stream);
 
+// Every kernel launch of this library is counted (aclsp_b200_kernel_launches reads the total): the
+// benchmark reports how many of the library's kernels make up a step.
+void AclspCountLaunches(unsigned n);
+
 #endif  // ACLSPARSE_B200_PLAN_KERNELS_H_

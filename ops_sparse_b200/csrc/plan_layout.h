@@ -134,4 +134,32 @@ static inline ACLSP_HD uint32_t aclspTileClass(uint32_t nr, uint32_t nt, uint32_
     return cls;
 }
 
+/* op(A) = transpose: the external buffer holds the plan of the TRANSPOSED matrix (whose row offsets,
+ * at ACLSP_HEADER_BYTES as in every plan, are the transpose's own row offsets) and behind it the rest of
+ * the transpose: its column indices, the permutation that carries the values over, the permuted
+ * values (rewritten by every product; during the build the same words hold the row of every entry),
+ * the per-column cursors of the build (afterwards the list of columns too long for a warp to sort)
+ * and the partial sums of the scan.  rowsT = columns of A. */
+typedef struct AclspTransposeLayout {
+    uint64_t rowPtrOff;
+    uint64_t colIndOff;
+    uint64_t permOff;
+    uint64_t valuesOff;
+    uint64_t cursorOff;
+    uint64_t scanOff;
+    uint64_t totalBytes;
+} AclspTransposeLayout;
+
+static inline ACLSP_HD void aclspTransposeLayout(uint64_t rowsT, uint64_t nnz, uint64_t planBytes,
+                                                 AclspTransposeLayout* out)
+{
+    out->rowPtrOff = ACLSP_HEADER_BYTES;
+    out->colIndOff = aclspAlignUp(planBytes);
+    out->permOff = aclspAlignUp(out->colIndOff + 4u * nnz);
+    out->valuesOff = aclspAlignUp(out->permOff + 4u * nnz);
+    out->cursorOff = aclspAlignUp(out->valuesOff + 4u * nnz);
+    out->scanOff = aclspAlignUp(out->cursorOff + 4u * (rowsT + 2u));
+    out->totalBytes = aclspAlignUp(out->scanOff + 4u * (rowsT / 512u + 16u));
+}
+
 #endif /* ACLSPARSE_B200_PLAN_LAYOUT_H_ */

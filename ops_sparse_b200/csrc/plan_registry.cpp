@@ -17,7 +17,9 @@
 #include <mutex>
 #include <unordered_map>
 
+#include "aclsparse_b200_kernels.h"
 #include "internal.h"
+#include "plan_kernels.h"
 
 namespace {
 
@@ -74,4 +76,18 @@ bool AclspPlanIsCurrent(const void* buffer, uint64_t serial)
     std::lock_guard<std::mutex> lock(r.mutex);
     const auto it = r.entries.find(buffer);
     return it != r.entries.end() && it->second.serial == serial;
+}
+
+namespace {
+std::atomic<uint64_t> gLaunches{0};
+}
+
+void AclspCountLaunches(unsigned n)
+{
+    gLaunches.fetch_add(n, std::memory_order_relaxed);
+}
+
+extern "C" uint64_t aclsp_b200_kernel_launches(void)
+{
+    return gLaunches.load(std::memory_order_relaxed);
 }

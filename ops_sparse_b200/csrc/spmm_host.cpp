@@ -6,7 +6,10 @@
  * :1903-1965; ValidateSpmmInputs :474-568).
  *
  * Differences that a caller can observe:
- *  - op(A) = transpose / conjugate transpose is answered with NOT_SUPPORTED;
+ *  - op(A) = transpose (and conjugate transpose: the data is real) builds the transposed matrix in
+ *    the external buffer during preprocessing, on the device, and multiplies with it (the reference
+ *    builds a CSC copy on the host, spmm_csr_mat.cpp:212-315); the buffer then needs about 12 bytes
+ *    per non-zero more;
  *  - only fp32 A, B, C with an fp32 compute type is accepted;
  *  - the buffer must be 64-byte aligned (INVALID_VALUE otherwise) and its size
  *    covers the B200 plan, not the reference's reorder table;
@@ -117,10 +120,6 @@ aclsparseStatus_t CheckInputs(const aclsparseSpMatDescr* a, const aclsparseDnMat
     if (b->ld < bLd || c->ld < cLd) {
         return ACL_SPARSE_STATUS_INVALID_VALUE;
     }
-    if (opA != ACL_SPARSE_OP_NON_TRANSPOSE) {
-        ACLSP_LOGE(kApi, "op(A) = transpose is not implemented on this build");
-        return ACL_SPARSE_STATUS_NOT_SUPPORTED;
-    }
     if (a->ptrStride != 1 || a->idxStride != 1 || a->valueStride != 1) {
         ACLSP_LOGE(kApi, "strided CSR arrays are not supported by SpMM");
         return ACL_SPARSE_STATUS_NOT_SUPPORTED;
@@ -157,9 +156,27 @@ aclsparseStatus_t CheckBuffer(const void* buffer)
     return ACL_SPARSE_STATUS_SUCCESS;
 }
 
-bool PlanMatches(const aclsparseSpMatDescr* a, uint64_t denseCols, const void* buffer, const aclsparseContext* h)
+// Size and offsets of what the external buffer holds: the plan of A, or for op(A) = transpose the plan of
+// the transposed matrix followed by the transpose itself.
+uint64_t BufferLayout(const aclsparseSpMatDescr* a, uint64_t denseCols, bool transposed, AclspTransposeLayout* tl)
+{
+    AclspPlanLayout layout;
+    if (!transposed) {
+        aclspSpmmLayout(a->rows, a->nnz, denseCols, &layout);
+        return layout.totalBytes;
+    }
+    aclspSpmmLayout(a->cols, a->nnz, denseCols, &layout);
+    aclspTransposeLayout(a->cols, a->nnz, layout.totalBytes, tl);
+    return tl->totalBytes;
+}
+
+bool PlanMatches(const aclsparseSpMatDescr* a, uint64_t denseCols, const void* buffer, const aclsparseContext* h,
+                 bool transposed)
 {
     const SpmmPlanRecord& p = a->spmm;
+    if (p.transposed != transposed || (transposed && p.colIndices != a->idxs)) {
+        return false;
+    }
     // Only a plan from an explicit Preprocess call is reused, and only while no later plan build (of this
     // or any other descriptor, SpMM or SpMV) went into the same buffer.
     return a->activeBuffer == buffer && p.buffer == buffer && p.fromPreprocess && AclspPlanIsCurrent(buffer, p.serial) &&
@@ -169,12 +186,25 @@ bool PlanMatches(const aclsparseSpMatDescr* a, uint64_t denseCols, const void* b
 }
 
 aclsparseStatus_t BuildPlan(aclsparseContext* h, aclsparseSpMatDescr* a, uint64_t denseCols, void* buffer,
-                            bool fromPreprocess)
+                            bool fromPreprocess, bool transposed)
 {
     (void)cudaGetLastError();
-    spmm_b200_preprocess_kernel_do(a->ptrs, buffer, static_cast<uint32_t>(a->rows), static_cast<uint32_t>(a->cols),
-                                   static_cast<uint32_t>(a->nnz), static_cast<uint32_t>(denseCols),
-                                   static_cast<int32_t>(a->baseType), h->stream);
+    if (transposed) {
+        // The transpose first (its row offsets land where a plan keeps them), then the plan of the
+        // transposed matrix over those offsets, in place.
+        AclspTransposeLayout tl;
+        (void)BufferLayout(a, denseCols, true, &tl);
+        aclsp_b200_transpose_build_kernel_do(a->ptrs, a->idxs, static_cast<uint32_t>(a->rows),
+                                             static_cast<uint32_t>(a->cols), static_cast<uint32_t>(a->nnz),
+                                             static_cast<int32_t>(a->baseType), 1, 1, buffer, &tl, h->stream);
+        spmm_b200_preprocess_kernel_do(static_cast<const unsigned char*>(buffer) + tl.rowPtrOff, buffer,
+                                       static_cast<uint32_t>(a->cols), static_cast<uint32_t>(a->rows),
+                                       static_cast<uint32_t>(a->nnz), static_cast<uint32_t>(denseCols), 0, h->stream);
+    } else {
+        spmm_b200_preprocess_kernel_do(a->ptrs, buffer, static_cast<uint32_t>(a->rows),
+                                       static_cast<uint32_t>(a->cols), static_cast<uint32_t>(a->nnz),
+                                       static_cast<uint32_t>(denseCols), static_cast<int32_t>(a->baseType), h->stream);
+    }
     const cudaError_t err = cudaPeekAtLastError();
     if (err != cudaSuccess) {
         ACLSP_LOGE(kApi, "preprocess enqueue failed: %s", cudaGetErrorString(err));
@@ -184,6 +214,8 @@ aclsparseStatus_t BuildPlan(aclsparseContext* h, aclsparseSpMatDescr* a, uint64_
     p.serial = AclspPublishPlan(buffer);
     p.fromPreprocess = fromPreprocess;
     p.buffer = buffer;
+    p.transposed = transposed;
+    p.colIndices = a->idxs;
     p.rowOffsets = a->ptrs;
     p.rows = a->rows;
     p.cols = a->cols;
@@ -224,9 +256,9 @@ extern "C" aclsparseStatus_t aclsparseSpMMGetBufferSize(aclsparseHandle_t handle
     if (st != ACL_SPARSE_STATUS_SUCCESS) {
         return st;
     }
-    AclspPlanLayout layout;
-    aclspSpmmLayout(matA->rows, matA->nnz, static_cast<uint64_t>(matC->cols), &layout);
-    *size = static_cast<size_t>(layout.totalBytes);
+    AclspTransposeLayout tl;
+    *size = static_cast<size_t>(BufferLayout(matA, static_cast<uint64_t>(matC->cols),
+                                             opA != ACL_SPARSE_OP_NON_TRANSPOSE, &tl));
     return ACL_SPARSE_STATUS_SUCCESS;
 }
 
@@ -249,7 +281,8 @@ extern "C" aclsparseStatus_t aclsparseSpMMPreprocess(aclsparseHandle_t handle, a
     if (st != ACL_SPARSE_STATUS_SUCCESS) {
         return st;
     }
-    return BuildPlan(handle, const_cast<aclsparseSpMatDescr*>(matA), static_cast<uint64_t>(matC->cols), buffer, true);
+    return BuildPlan(handle, const_cast<aclsparseSpMatDescr*>(matA), static_cast<uint64_t>(matC->cols), buffer, true,
+                     opA != ACL_SPARSE_OP_NON_TRANSPOSE);
 }
 
 extern "C" aclsparseStatus_t aclsparseSpMM(aclsparseHandle_t handle, aclsparseOperation_t opA,
@@ -274,18 +307,35 @@ extern "C" aclsparseStatus_t aclsparseSpMM(aclsparseHandle_t handle, aclsparseOp
     const uint64_t n = static_cast<uint64_t>(matC->cols);
     // Preprocess is optional: without a matching plan in this buffer it is
     // built here, on the same stream, ahead of the product.
-    if (!PlanMatches(a, n, buffer, handle)) {
-        st = BuildPlan(handle, a, n, buffer, false);
+    const bool transposed = opA != ACL_SPARSE_OP_NON_TRANSPOSE;
+    if (!PlanMatches(a, n, buffer, handle, transposed)) {
+        st = BuildPlan(handle, a, n, buffer, false, transposed);
         if (st != ACL_SPARSE_STATUS_SUCCESS) {
             return st;
         }
     }
 
+    (void)cudaGetLastError();  // an enqueue failure below is this call's
     AclspSpmmParams params{};
+    const void* colInd = a->idxs;
+    const void* values = a->values;
     params.rows = static_cast<uint32_t>(a->rows);
     params.cols = static_cast<uint32_t>(a->cols);
     params.nnz = static_cast<uint32_t>(a->nnz);
     params.indexBase = static_cast<uint32_t>(a->baseType);
+    if (transposed) {
+        // The product runs on the transposed matrix in the buffer: base 0, its values gathered from the
+        // caller's through the permutation, now, so that they are the current ones.
+        AclspTransposeLayout tl;
+        (void)BufferLayout(a, n, true, &tl);
+        aclsp_b200_transpose_values_kernel_do(a->values, 1, static_cast<uint32_t>(a->cols),
+                                              static_cast<uint32_t>(a->nnz), buffer, &tl, handle->stream);
+        colInd = static_cast<const unsigned char*>(buffer) + tl.colIndOff;
+        values = static_cast<const unsigned char*>(buffer) + tl.valuesOff;
+        params.rows = static_cast<uint32_t>(a->cols);
+        params.cols = static_cast<uint32_t>(a->rows);
+        params.indexBase = 0;
+    }
     params.n = static_cast<uint32_t>(n);
     params.opB = opB == ACL_SPARSE_OP_NON_TRANSPOSE ? 0u : 1u;  // real data: H is T
     params.orderB = static_cast<uint32_t>(matB->order);
@@ -310,8 +360,7 @@ extern "C" aclsparseStatus_t aclsparseSpMM(aclsparseHandle_t handle, aclsparseOp
         }
     }
 
-    (void)cudaGetLastError();
-    spmm_b200_kernel_do(a->idxs, a->values, matB->values, matC->values, buffer, &params, handle->stream);
+    spmm_b200_kernel_do(colInd, values, matB->values, matC->values, buffer, &params, handle->stream);
     const cudaError_t err = cudaPeekAtLastError();
     if (err != cudaSuccess) {
         ACLSP_LOGE(kApi, "kernel enqueue failed: %s", cudaGetErrorString(err));

@@ -46,6 +46,7 @@
 #include <cuda_runtime.h>
 
 #include "aclsparse_b200_kernels.h"
+#include "plan_kernels.h"
 #include "plan_layout.h"
 
 namespace {
@@ -549,6 +550,7 @@ void Launch(const void* colInd, const void* values, const void* b, void* c, cons
     // and per device; the attribute is cheap to set, so it is set every time.
     cudaFuncSetAttribute(SpmmTileKernel<VW, kStageB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                          static_cast<int>(smem));
+    AclspCountLaunches(1);
     SpmmTileKernel<VW, kStageB><<<plan.numTiles, kThreads, smem, s>>>(
         static_cast<const int32_t*>(colInd), static_cast<const float*>(values), static_cast<const float*>(b),
         static_cast<float*>(c), plan, p, ds);
@@ -611,5 +613,6 @@ extern "C" void spmm_b200_kernel_do(const void* colInd, const void* values, cons
     }
     uint32_t blocks = (plan.numTiles + 7u) / 8u;
     blocks = blocks > 148u * 8u ? 148u * 8u : blocks;
+    AclspCountLaunches(1);
     SpmmCarryFixupKernel<<<blocks, 256, 0, s>>>(static_cast<float*>(c), plan, p, ds);
 }

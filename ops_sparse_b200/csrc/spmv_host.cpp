@@ -7,7 +7,9 @@
  * :357-368, three entry points :526-678).
  *
  * Differences that a caller can observe:
- *  - op(A) = transpose / conjugate transpose is answered with NOT_SUPPORTED;
+ *  - op(A) = transpose (and conjugate transpose, the same thing for real data) builds the transposed
+ *    matrix in the external buffer during preprocessing and multiplies with it: the buffer is much
+ *    larger (about 12 bytes per non-zero) and the result is bit-reproducible for every algorithm value;
  *  - only fp32 A, x, y with an fp32 compute type is accepted (the reference's
  *    other dtype combinations are answered with NOT_SUPPORTED);
  *  - the buffer size covers the B200 plan (row offsets + tile splits + row
@@ -156,10 +158,7 @@ aclsparseStatus_t CheckMatrix(const aclsparseSpMatDescr* mat, const aclsparseDnV
                    static_cast<int>(y->valueType), static_cast<int>(computeType));
         return ACL_SPARSE_STATUS_NOT_SUPPORTED;
     }
-    if (IsTranspose(opA)) {
-        ACLSP_LOGE(kApi, "op(A) = transpose is not implemented on this build");
-        return ACL_SPARSE_STATUS_NOT_SUPPORTED;
-    }
+    (void)opA;
     if (!StrideFits(mat->rows + 1u, mat->ptrStride, sizeof(int32_t)) ||
         !StrideFits(mat->nnz, mat->idxStride, sizeof(int32_t)) ||
         !StrideFits(mat->nnz, mat->valueStride, ElementBytes(mat->valueType)) ||
@@ -215,7 +214,7 @@ aclsparseStatus_t CheckStorage(const aclsparseSpMatDescr* mat, const aclsparseDn
                                const aclsparseDnVecDescr* y)
 {
     if ((mat->rows > 0 && mat->ptrs == nullptr) || (mat->nnz > 0 && (mat->idxs == nullptr || mat->values == nullptr)) ||
-        (mat->cols > 0 && x->values == nullptr) || (mat->rows > 0 && y->values == nullptr)) {
+        (x->nums > 0 && x->values == nullptr) || (y->nums > 0 && y->values == nullptr)) {
         ACLSP_LOGE(kApi, "required storage is unbound");
         return ACL_SPARSE_STATUS_INVALID_VALUE;
     }
@@ -237,6 +236,20 @@ aclsparseStatus_t CheckWorkspace(const void* buffer)
         return ACL_SPARSE_STATUS_INVALID_VALUE;
     }
     return ACL_SPARSE_STATUS_SUCCESS;
+}
+
+// Size and offsets of what the external buffer holds: the plan of A, or for op(A) = transpose the plan of
+// the transposed matrix followed by the transpose itself.
+uint64_t BufferLayout(const aclsparseSpMatDescr* mat, bool transposed, AclspTransposeLayout* tl)
+{
+    AclspPlanLayout layout;
+    if (!transposed) {
+        aclspSpmvLayout(mat->rows, mat->nnz, &layout);
+        return layout.totalBytes;
+    }
+    aclspSpmvLayout(mat->cols, mat->nnz, &layout);
+    aclspTransposeLayout(mat->cols, mat->nnz, layout.totalBytes, tl);
+    return tl->totalBytes;
 }
 
 bool PlanMatches(const aclsparseSpMatDescr* mat, const aclsparseDnVecDescr* x, const aclsparseDnVecDescr* y,
@@ -288,12 +301,26 @@ void RecordPlan(aclsparseSpMatDescr* mat, const aclsparseDnVecDescr* x, const ac
 
 // Enqueues the plan-building kernels.  An enqueue failure is attributed to
 // this launch only: the sticky-free last error is cleared first, then peeked.
-aclsparseStatus_t LaunchPreprocess(const aclsparseContext* h, aclsparseSpMatDescr* mat, void* buffer)
+aclsparseStatus_t LaunchPreprocess(const aclsparseContext* h, aclsparseSpMatDescr* mat, void* buffer, bool transposed)
 {
     (void)cudaGetLastError();
-    spmv_b200_preprocess_kernel_do(mat->ptrs, buffer, static_cast<uint32_t>(mat->rows),
-                                   static_cast<uint32_t>(mat->cols), static_cast<uint32_t>(mat->nnz),
-                                   static_cast<int32_t>(mat->baseType), mat->ptrStride, h->stream);
+    if (transposed) {
+        // The transpose first (its row offsets land where a plan keeps them), then the plan of the
+        // transposed matrix over those offsets, in place.
+        AclspTransposeLayout tl;
+        (void)BufferLayout(mat, true, &tl);
+        aclsp_b200_transpose_build_kernel_do(mat->ptrs, mat->idxs, static_cast<uint32_t>(mat->rows),
+                                             static_cast<uint32_t>(mat->cols), static_cast<uint32_t>(mat->nnz),
+                                             static_cast<int32_t>(mat->baseType), mat->ptrStride, mat->idxStride,
+                                             buffer, &tl, h->stream);
+        spmv_b200_preprocess_kernel_do(static_cast<const unsigned char*>(buffer) + tl.rowPtrOff, buffer,
+                                       static_cast<uint32_t>(mat->cols), static_cast<uint32_t>(mat->rows),
+                                       static_cast<uint32_t>(mat->nnz), 0, 1, h->stream);
+    } else {
+        spmv_b200_preprocess_kernel_do(mat->ptrs, buffer, static_cast<uint32_t>(mat->rows),
+                                       static_cast<uint32_t>(mat->cols), static_cast<uint32_t>(mat->nnz),
+                                       static_cast<int32_t>(mat->baseType), mat->ptrStride, h->stream);
+    }
     // The longest row, which the pass has just written into the plan header, is sent to pinned host
     // memory in stream order; products look there to pick their kernel and never wait for it.
     mat->spmv.longestRow = AclspAcquireHostSlot();
@@ -326,9 +353,8 @@ extern "C" aclsparseStatus_t aclsparseSpMVGetBufferSize(aclsparseHandle_t handle
     if (st != ACL_SPARSE_STATUS_SUCCESS) {
         return st;
     }
-    AclspPlanLayout layout;
-    aclspSpmvLayout(matA->rows, matA->nnz, &layout);
-    *bufferSize = static_cast<size_t>(layout.totalBytes);
+    AclspTransposeLayout tl;
+    *bufferSize = static_cast<size_t>(BufferLayout(matA, IsTranspose(opA), &tl));
     return ACL_SPARSE_STATUS_SUCCESS;
 }
 
@@ -343,8 +369,9 @@ extern "C" aclsparseStatus_t aclsparseSpMVPreprocess(aclsparseHandle_t handle, a
         return st;
     }
     auto* mat = const_cast<aclsparseSpMatDescr*>(matA);
-    // Preprocessing reads the row offsets only; values and vectors may be bound later.
-    if (mat->rows > 0 && mat->ptrs == nullptr) {
+    // Preprocessing reads the row offsets only (and, to build a transpose, the column indices);
+    // values and vectors may be bound later.
+    if ((mat->rows > 0 && mat->ptrs == nullptr) || (IsTranspose(opA) && mat->nnz > 0 && mat->idxs == nullptr)) {
         return ACL_SPARSE_STATUS_INVALID_VALUE;
     }
     st = CheckWorkspace(externalBuffer);
@@ -356,8 +383,8 @@ extern "C" aclsparseStatus_t aclsparseSpMVPreprocess(aclsparseHandle_t handle, a
     if (mat->activeBuffer == externalBuffer) {
         mat->activeBuffer = nullptr;
     }
-    if (mat->rows > 0) {
-        st = LaunchPreprocess(handle, mat, externalBuffer);
+    if (vecY->nums > 0) {
+        st = LaunchPreprocess(handle, mat, externalBuffer, IsTranspose(opA));
         if (st != ACL_SPARSE_STATUS_SUCCESS) {
             return st;
         }
@@ -384,9 +411,10 @@ extern "C" aclsparseStatus_t aclsparseSpMV(aclsparseHandle_t handle, aclsparseOp
     if (st != ACL_SPARSE_STATUS_SUCCESS) {
         return st;
     }
-    if (mat->rows == 0) {  // nothing to write
+    if (vecY->nums == 0) {  // nothing to write
         return ACL_SPARSE_STATUS_SUCCESS;
     }
+    const bool transposed = IsTranspose(opA);
     // Preprocess is optional.  Without a matching plan from a Preprocess call in this buffer the
     // plan is (re)built here, on the same stream and ahead of the product (a few O(rows) kernels),
     // so that a caller who never preprocesses, or who let another operator or another matrix
@@ -395,20 +423,38 @@ extern "C" aclsparseStatus_t aclsparseSpMV(aclsparseHandle_t handle, aclsparseOp
         if (mat->activeBuffer == externalBuffer) {
             mat->activeBuffer = nullptr;
         }
-        st = LaunchPreprocess(handle, mat, externalBuffer);
+        st = LaunchPreprocess(handle, mat, externalBuffer, transposed);
         if (st != ACL_SPARSE_STATUS_SUCCESS) {
             return st;
         }
         RecordPlan(mat, vecX, vecY, opA, computeType, alg, externalBuffer, handle, false);
     }
 
+    (void)cudaGetLastError();  // an enqueue failure below is this call's
     AclspSpmvParams params{};
+    const void* colInd = mat->idxs;
+    const void* values = mat->values;
     params.rows = static_cast<uint32_t>(mat->rows);
     params.cols = static_cast<uint32_t>(mat->cols);
     params.nnz = static_cast<uint32_t>(mat->nnz);
     params.indexBase = static_cast<uint32_t>(mat->baseType);
     params.colIndStride = mat->idxStride;
     params.valuesStride = mat->valueStride;
+    if (transposed) {
+        // The product runs on the transposed matrix in the buffer: base 0, unit strides, its values
+        // gathered from the caller's through the permutation, now, so that they are the current ones.
+        AclspTransposeLayout tl;
+        (void)BufferLayout(mat, true, &tl);
+        aclsp_b200_transpose_values_kernel_do(mat->values, mat->valueStride, static_cast<uint32_t>(mat->cols),
+                                              static_cast<uint32_t>(mat->nnz), externalBuffer, &tl, handle->stream);
+        colInd = static_cast<const unsigned char*>(externalBuffer) + tl.colIndOff;
+        values = static_cast<const unsigned char*>(externalBuffer) + tl.valuesOff;
+        params.rows = static_cast<uint32_t>(mat->cols);
+        params.cols = static_cast<uint32_t>(mat->rows);
+        params.indexBase = 0;
+        params.colIndStride = 1;
+        params.valuesStride = 1;
+    }
     params.xStride = vecX->stride;
     params.yStride = vecY->stride;
     if (handle->pointerMode == ACL_SPARSE_POINTER_MODE_DEVICE) {
@@ -434,9 +480,7 @@ extern "C" aclsparseStatus_t aclsparseSpMV(aclsparseHandle_t handle, aclsparseOp
         }
     }
 
-    (void)cudaGetLastError();
-    spmv_b200_kernel_do(mat->idxs, mat->values, vecX->values, vecY->values, externalBuffer, &params,
-                        handle->stream);
+    spmv_b200_kernel_do(colInd, values, vecX->values, vecY->values, externalBuffer, &params, handle->stream);
     const cudaError_t err = cudaPeekAtLastError();
     if (err != cudaSuccess) {
         ACLSP_LOGE(kApi, "kernel enqueue failed: %s", cudaGetErrorString(err));

@@ -71,6 +71,7 @@
 #include <cuda_runtime.h>
 
 #include "aclsparse_b200_kernels.h"
+#include "plan_kernels.h"
 #include "plan_layout.h"
 
 namespace {
@@ -129,12 +130,19 @@ __device__ __forceinline__ Scalars LoadScalars(const AclspSpmvParams& p)
     return s;
 }
 
-// beta == 0 must not read y: it may hold NaN or be uninitialised.
-__device__ __forceinline__ float StoreRow(float* __restrict__ y, int64_t index, double sum, const Scalars& s)
+// Row `row` of the result: alpha * sum + beta * (the vector beta scales), written to `at`.  The
+// vector beta scales is y itself, or p.betaSource when the product writes a vector of its own
+// (the SpMVOp form Z = alpha*A*X + beta*Y).  beta == 0 must not read it: it may hold NaN, be
+// uninitialised or be absent.
+__device__ __forceinline__ float StoreRow(float* at, int64_t row, double sum, const Scalars& s, const AclspSpmvParams& p)
 {
-    const double r = s.betaZero ? s.alpha * sum : s.alpha * sum + s.beta * static_cast<double>(y[index]);
+    double r = s.alpha * sum;
+    if (!s.betaZero) {
+        const float* from = p.betaSource != nullptr ? p.betaSource + row * p.betaSourceStride : at;
+        r += s.beta * static_cast<double>(*from);
+    }
     const float out = static_cast<float>(r);
-    y[index] = out;
+    *at = out;
     return out;
 }
 
@@ -285,7 +293,7 @@ __device__ __forceinline__ void ReduceTile(const StagedTile& st, float* __restri
             plan.carry[2 * t + 1] = sum;
         } else {
             float* at = y + static_cast<int64_t>(i0 + k) * p.yStride;
-            const float out = StoreRow(at, 0, sum, sc);
+            const float out = StoreRow(at, i0 + k, sum, sc, p);
             if (p.numMirrors != 0) {
                 if (batchMirrors) {
                     sOut[k] = out;
@@ -743,7 +751,7 @@ SpmvRowBlockKernel(const int32_t* __restrict__ colInd, const float* __restrict__
     };
     auto writeRow = [&](int row, double sum) {
         float* at = y + static_cast<int64_t>(row) * p.yStride;
-        const float out = StoreRow(at, 0, sum, sc);
+        const float out = StoreRow(at, row, sum, sc, p);
         if (p.numMirrors != 0) {
             MirrorStore(at, out, p);  // 32 consecutive rows per warp: whole lines on the links
         }
@@ -887,7 +895,7 @@ SpmvCarryFixupKernel(float* __restrict__ y, SpmvPlanView plan, AclspSpmvParams p
     const Scalars sc = LoadScalars(p);
     auto writeRow = [&](int row, double sum) {
         float* at = y + static_cast<int64_t>(row) * p.yStride;
-        const float out = StoreRow(at, 0, sum, sc);
+        const float out = StoreRow(at, row, sum, sc, p);
         if (p.numMirrors != 0) {
             MirrorStore(at, out, p);
         }
@@ -972,6 +980,7 @@ void LaunchRowBlocks(const void* colInd, const void* values, const void* x, void
     uint32_t grid = static_cast<uint32_t>(sms) * ctasPerSm;
     const uint32_t needed = (numBlocks + kWarpsPerCta - 1u) / kWarpsPerCta;
     grid = grid < needed ? grid : needed;
+    AclspCountLaunches(1);
     kernel<<<grid > 0 ? grid : 1u, 32 * kWarpsPerCta, smem, s>>>(
         static_cast<const int32_t*>(colInd), static_cast<const float*>(values), static_cast<const float*>(x),
         static_cast<float*>(y), plan, p, maxRowLen, waitFailures, cap, checkPlan ? 1 : 0);
@@ -1034,15 +1043,18 @@ extern "C" void spmv_b200_kernel_do(const void* colInd, const void* values, cons
     }
     const uint32_t tileCap = checkPlan ? cap : 0u;
     if (vector) {
+        AclspCountLaunches(1);
         SpmvTileKernel<true><<<plan.numTiles, kThreads, 0, s>>>(
             static_cast<const int32_t*>(colInd), static_cast<const float*>(values), static_cast<const float*>(x),
             static_cast<float*>(y), plan, p, maxRowLen, tileCap);
     } else {
+        AclspCountLaunches(1);
         SpmvTileKernel<false><<<plan.numTiles, kThreads, 0, s>>>(
             static_cast<const int32_t*>(colInd), static_cast<const float*>(values), static_cast<const float*>(x),
             static_cast<float*>(y), plan, p, maxRowLen, tileCap);
     }
     const uint32_t fixupWarps = (plan.numTiles + 31u) / 32u;
+    AclspCountLaunches(1);
     SpmvCarryFixupKernel<<<(fixupWarps + kWarps - 1u) / kWarps, kThreads, 0, s>>>(static_cast<float*>(y), plan, p,
                                                                                  maxRowLen, tileCap);
 }

@@ -15,8 +15,10 @@
  * a device symbol: host code cannot pass `gScratch` itself to a kernel, it has
  * to ask the runtime for the symbol's device address, once per device, with
  * that device current.  The first call on a device does this
- * (cudaGetSymbolAddress) and caches the answer; make that first call outside
- * any stream capture.
+ * (cudaGetSymbolAddress) and caches the answer.  Under lazy module loading
+ * that first call is also what loads this library's device code, the array
+ * with it: it can take device memory once.  Make it at start-up, outside any
+ * stream capture; only the calls after it are allocation-free.
  *
  * All calls on a device share the one array, and it keeps the contents of the
  * previous call.  Nothing in it has to start at zero - every call rewrites the

@@ -166,6 +166,8 @@ class _GraphedStep:
     """
 
     _graph = None
+    _step_launches = None
+    _captured_launches = 0
     _product_graph = None
     _out = None
     _group = None
@@ -195,8 +197,10 @@ class _GraphedStep:
                 body()
             side.synchronize()
             graph = torch.cuda.CUDAGraph()
+            before = int(L.lib().aclsp_b200_kernel_launches())
             with torch.cuda.graph(graph, stream=side):
                 body()
+            self._captured_launches = int(L.lib().aclsp_b200_kernel_launches()) - before
         finally:
             self.handle.set_stream(torch.cuda.current_stream().cuda_stream)
         return graph
@@ -206,6 +210,7 @@ class _GraphedStep:
         if self._product is not None or (self.world > 1 and self.gather_mode == "nccl"):
             return False
         self._graph = (self._capture(lambda: self._eager_step(alpha, beta)), float(alpha), float(beta))
+        self._step_launches = self._captured_launches
         return True
 
     def capture_product(self, alpha: float, beta: float):
@@ -217,12 +222,14 @@ class _GraphedStep:
         return graph.replay
 
     # ---- what the benchmark reports about the operator
-    def launches_per_step(self) -> int:
-        """Kernels of this library launched per step on this rank (kernels that find nothing to do included)."""
-        n = len(self.kernel_names.split(" + ")) if self.r1 > self.r0 else 0
-        if self.world > 1 and self.gather_mode != "nccl":
-            n += 1 if self.gather_mode in ("fused", "multicast") else 2  # the barrier kernel (+ the push kernel)
-        return n
+    def launches_per_step(self, alpha: float, beta: float) -> int:
+        """Kernels of this library launched per step on this rank, counted by the library itself: the launches
+        recorded into the step's graph, or those of one eager step where the step is not captured."""
+        if self._graph is not None and self._step_launches is not None:
+            return self._step_launches
+        before = int(L.lib().aclsp_b200_kernel_launches())
+        self._eager_step(alpha, beta)
+        return int(L.lib().aclsp_b200_kernel_launches()) - before
 
     # ---- inputs that arrive from the host: every rank uploads one share, the shares are all-gathered
     def pinned_input_share(self, cfg: dict) -> torch.Tensor:

@@ -29,7 +29,8 @@ def build(ref: bool = True) -> None:
     """Compile the oracle (and the reference-backed library when the reference checkout exists)."""
     subprocess.run(["make", "-C", _HERE, "all"], check=True, capture_output=True)
     if ref:
-        subprocess.run(["make", "-C", _HERE, "ref"], check=True, capture_output=True)
+        where = os.environ.get("OPS_SPARSE_REFERENCE", os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference"))
+        subprocess.run(["make", "-C", _HERE, "ref", f"REF={where}"], check=True, capture_output=True)
 
 
 def _load():
@@ -221,6 +222,35 @@ def longest_row(row_ptr) -> int:
     """Longest row as the SpMV preprocessing pass records it in the plan header (a negative length counts as 0)."""
     d = np.diff(np.asarray(row_ptr, dtype=np.int64))
     return int(max(d.max(), 0)) if d.size else 0
+
+
+def transpose_plan_layout(rows_t: int, nnz: int, plan_bytes: int) -> dict:
+    """Offsets of the transpose behind the plan of the transposed matrix (twin of aclspTransposeLayout)."""
+    col_ind_off = _align64(plan_bytes)
+    perm_off = _align64(col_ind_off + 4 * nnz)
+    values_off = _align64(perm_off + 4 * nnz)
+    cursor_off = _align64(values_off + 4 * nnz)
+    scan_off = _align64(cursor_off + 4 * (rows_t + 2))
+    total = _align64(scan_off + 4 * (rows_t // 512 + 16))
+    return dict(row_ptr_off=HEADER_BYTES, col_ind_off=col_ind_off, perm_off=perm_off, values_off=values_off,
+                cursor_off=cursor_off, scan_off=scan_off, total_bytes=total)
+
+
+def transpose_twin(row_ptr, col_ind, cols: int, index_base=0):
+    """CPU twin of the device transpose build: (row offsets, column indices, permutation) of A^T as CSR.
+    A stable counting sort by column: entries of one column keep their original order, entries whose
+    column is out of range are left out."""
+    rp = np.clip(np.asarray(row_ptr, dtype=np.int64) - index_base, 0, len(col_ind))
+    rows = rp.size - 1
+    lens = np.maximum(np.diff(rp), 0)
+    row_of = np.full(len(col_ind), -1, dtype=np.int64)
+    for r in np.flatnonzero(lens):
+        row_of[rp[r]:rp[r] + lens[r]] = r
+    c = np.asarray(col_ind, dtype=np.int64) - index_base
+    kept = np.flatnonzero((row_of >= 0) & (c >= 0) & (c < cols))
+    perm = kept[np.argsort(c[kept], kind="stable")]
+    row_ptr_t = np.concatenate([[0], np.cumsum(np.bincount(c[kept], minlength=cols))]).astype(np.int32)
+    return row_ptr_t, row_of[perm].astype(np.int32), perm.astype(np.int32)
 
 
 def row_block_bounds(row_ptr, nnz: int, parts: int, index_base=0) -> np.ndarray:

@@ -240,8 +240,13 @@ def test_spmv_buffer_size_and_status_precedence(lib, handle):
     assert lib.aclsparseSpMVGetBufferSize(*spmv_args(handle, m64, x, y), byref(size)) == L.NOT_SUPPORTED
     mh = make_csr(lib, dtype=L.ACL_FLOAT16)
     assert lib.aclsparseSpMVGetBufferSize(*spmv_args(handle, mh, x, y), byref(size)) == L.NOT_SUPPORTED
+    # op(A) = T / H: x has one entry per row of A and y one per column; the buffer also holds the transpose
     xt, yt = make_vec(lib, 2), make_vec(lib, 3, FAKE[4])
-    assert lib.aclsparseSpMVGetBufferSize(*spmv_args(handle, mat, xt, yt, op=L.OP_T), byref(size)) == L.NOT_SUPPORTED
+    from oracle import oracle as O
+    for op in (L.OP_T, L.OP_H):
+        assert lib.aclsparseSpMVGetBufferSize(*spmv_args(handle, mat, xt, yt, op=op), byref(size)) == L.SUCCESS
+        assert size.value == O.transpose_plan_layout(3, 3, O.spmv_plan_layout(3, 3)["total_bytes"])["total_bytes"]
+    assert lib.aclsparseSpMVGetBufferSize(*spmv_args(handle, mat, x, y, op=L.OP_T), byref(size)) == L.INVALID_VALUE
     # the three accepted algorithms, and unbound storage is fine for a size query
     unbound = make_csr(lib, ptrs=None, idx=None, val=None)
     xu, yu = make_vec(lib, 3, None), make_vec(lib, 2, None)
@@ -382,3 +387,13 @@ def test_create_destroy_loop(lib):
         m, x = make_csr(lib), make_vec(lib, 3)
         assert lib.aclsparseDestroySpMat(m) == L.SUCCESS
         assert lib.aclsparseDestroyDnVec(x) == L.SUCCESS
+
+
+def test_library_exports_only_its_c_api():
+    """Hidden visibility: the dynamic symbol table holds the C entry points and nothing else of this library."""
+    import subprocess
+    out = subprocess.run(["nm", "-D", "--defined-only", L.LIB_PATH], capture_output=True, text=True, check=True).stdout
+    names = [line.split()[-1] for line in out.splitlines() if line.strip()]
+    assert names, "no dynamic symbols found"
+    stray = [n for n in names if not (n.startswith("aclsparse") or n.startswith("aclsp_") or "_b200_" in n)]
+    assert not stray, f"internal symbols exported: {stray[:10]}"

@@ -304,3 +304,47 @@ def test_shared_workspace_between_spmv_and_spmm(kats):
         mv()  # must not trust SpMM metadata in the buffer
         torch.cuda.synchronize()
         np.testing.assert_allclose(d_y.cpu().numpy(), [11, 8], atol=1e-5)
+
+
+# ------------------------------------------------------------------ op(A) = transpose --
+
+def _transpose_host(rp, ci, va, cols):
+    """A^T as CSR on the host (stable counting sort by column), for the oracle."""
+    rpt, cit, perm = O.transpose_twin(rp, ci, cols)
+    return rpt, cit, np.asarray(va, np.float32)[perm]
+
+
+@pytest.mark.parametrize("op_a", [L.OP_T, L.OP_H])
+@pytest.mark.parametrize("n", [1, 7, 64, 128])
+def test_transposed_a_vs_oracle(op_a, n):
+    """C = alpha * A^T * B + beta * C (reference cases: test/spmm/arch35/spmm_transpose_test.cpp): A is m x k,
+    B has m rows and C has k."""
+    rng = np.random.default_rng(50 + n)
+    m, k = 700, 500
+    lengths = np.concatenate([rng.integers(0, 25, m - 2), [400, 0]])
+    rp, ci = random_csr(rng, lengths, k)
+    va = rng.uniform(-1, 1, ci.size).astype(np.float32)
+    b = rng.uniform(-1, 1, (m, n)).astype(np.float32)
+    c0 = rng.uniform(-1, 1, (k, n)).astype(np.float32)
+    from ops_sparse_b200 import api
+    d_rp, d_ci, d_va, d_b, d_c = dev(rp, np.int32), dev(ci, np.int32), dev(va), dev(b), dev(c0)
+    h = api.Handle()
+    mat = api.CsrMatrix(m, k, d_rp, d_ci, d_va, nnz=ci.size)
+    op = api.SpMM(h, mat, api.DnMat(m, n, n, d_b), api.DnMat(k, n, n, d_c), op_a=op_a)
+    rpt, cit, vat = _transpose_host(rp, ci, va, k)
+    truth = O.spmm_f64(rpt, cit, vat, b, n, c0, n, n, m, 0.75, -0.5)
+    for pre in (True, False):
+        d_c.copy_(torch.from_numpy(c0))
+        if pre:
+            op.preprocess(0.75, -0.5)
+        op(0.75, -0.5)
+        torch.cuda.synchronize()
+        assert_close(d_c.cpu().numpy(), truth, f"A^T n={n} preprocess={pre}")
+    # new values through the same plan
+    va2 = (va * 0.5 + 0.25).astype(np.float32)
+    d_va.copy_(torch.from_numpy(va2))
+    d_c.copy_(torch.from_numpy(c0))
+    op(0.75, -0.5)
+    torch.cuda.synchronize()
+    assert_close(d_c.cpu().numpy(), O.spmm_f64(rpt, cit, va2[O.transpose_twin(rp, ci, k)[2]], b, n, c0, n, n, m,
+                                               0.75, -0.5), f"A^T n={n}, new values")

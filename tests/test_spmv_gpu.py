@@ -368,3 +368,100 @@ def test_full_size_stencil_properties():
     case.d_x.mul_(2.0)
     twice = case.run(1.0, 0.0, preprocess=False)
     np.testing.assert_array_equal(twice, 2.0 * got)
+
+
+# ------------------------------------------------------------------ op(A) = transpose --
+
+def _transposed_case(rp, ci, va, x, y, cols, base=0, op=L.OP_T, alg=L.SPMV_ALG_DEFAULT):
+    """SpMV with op(A) = T: x has one entry per row of A, y one per column."""
+    case = SpmvCase.__new__(SpmvCase)
+    case.rows, case.cols, case.nnz = len(rp) - 1, cols, len(ci)
+    case.d_rp = dev(np.asarray(rp), np.int32)
+    case.d_ci = dev(np.asarray(ci), np.int32) if case.nnz else None
+    case.d_va = dev(np.asarray(va), np.float32) if case.nnz else None
+    case.d_x, case.d_y = dev(np.asarray(x), np.float32), dev(np.asarray(y), np.float32)
+    case.handle = api.Handle()
+    case.mat = api.CsrMatrix(case.rows, cols, case.d_rp, case.d_ci, case.d_va, base, nnz=case.nnz)
+    case.vx, case.vy = api.DnVec(case.d_x), api.DnVec(case.d_y)
+    case.op = api.SpMV(case.handle, case.mat, case.vx, case.vy, alg=alg, op=op)
+    return case
+
+
+def test_transposed_reference_fixture(kats):
+    """The reference's transposed cases of its 2x3 fixture (test/spmv/arch35/spmv_test.cpp:69-86, CSV rows with T)."""
+    hit = 0
+    for k in kats["spmv"]:
+        if k.get("op", "N") == "N":
+            continue
+        hit += 1
+        case = _transposed_case(k["row_ptr"], k["col_ind"], k["values"], k["x"], k["y"], k["cols"], base=k["base"])
+        got = case.run(k["alpha"], k["beta"])
+        np.testing.assert_allclose(got, np.array(k["expect"], np.float32), rtol=0, atol=1e-5, err_msg=k["name"])
+    # the fixture itself, spelled out, in case the known-answer file carries no transposed row
+    rp, ci, va = [0, 2, 3], [0, 2, 1], [2.0, 3.0, 4.0]
+    x, y = [1.0, 2.0], [1.0, 1.0, 1.0]
+    for op in (L.OP_T, L.OP_H):
+        got = _transposed_case(rp, ci, va, x, y, 3, op=op).run(2.0, 3.0)
+        np.testing.assert_allclose(got, [2 * 2 + 3, 2 * 8 + 3, 2 * 3 + 3], atol=1e-5)
+
+
+def test_transposed_plan_bit_exact():
+    """Row offsets, column indices and permutation of the transpose built on the device == the CPU twin."""
+    rng = np.random.default_rng(41)
+    shapes = [(rng.integers(0, 30, 5000), 3000), (np.clip(rng.zipf(2.0, 4000) * 3, 1, 2500), 2600),
+              (np.full(3000, 40), 50), (np.full(200, 900), 1000), (np.zeros(100, int), 70)]
+    for base in (0, 1):
+        for lengths, cols in shapes:
+            rp, ci = random_csr(rng, lengths, cols)
+            if ci.size:
+                ci = ci.copy()
+                ci[::97] = cols + 3            # out-of-range entries are left out of the transpose
+            case = _transposed_case(rp + base, ci + base, np.ones(ci.size, np.float32), np.ones(len(lengths), np.float32),
+                                    np.zeros(cols, np.float32), cols, base=base)
+            case.op.preprocess()
+            torch.cuda.synchronize()
+            ws = case.op.buffer.cpu().numpy()
+            plan = O.spmv_plan_layout(cols, ci.size)
+            lay = O.transpose_plan_layout(cols, ci.size, plan["total_bytes"])
+            assert ws.size == lay["total_bytes"]
+            rpt, cit, perm = O.transpose_twin(rp + base, ci + base, cols, base)
+            kept = int(rpt[-1])
+            assert np.array_equal(ws[lay["row_ptr_off"]:lay["row_ptr_off"] + 4 * (cols + 1)].view(np.int32), rpt)
+            assert np.array_equal(ws[lay["perm_off"]:lay["perm_off"] + 4 * kept].view(np.int32), perm)
+            assert np.array_equal(ws[lay["col_ind_off"]:lay["col_ind_off"] + 4 * kept].view(np.int32), cit)
+
+
+@pytest.mark.parametrize("name,rows", [("c1", None), ("c2", 40 ** 3), ("c3", 1 << 16)])
+def test_transposed_benchmark_shapes_vs_oracle(name, rows):
+    cfg = workloads.make(name, rows=rows)
+    rng = np.random.default_rng(7)
+    x = rng.standard_normal(cfg["rows"]).astype(np.float32)
+    y = rng.uniform(-1, 1, cfg["cols"]).astype(np.float32)
+    truth = O.spmv_transpose_f64(cfg["row_ptr"], cfg["col_ind"], cfg["values"], x, y, cfg["cols"], 1.5, 0.5)
+    case = _transposed_case(cfg["row_ptr"], cfg["col_ind"], cfg["values"], x, y, cfg["cols"])
+    got = case.run(1.5, 0.5)
+    assert_close(got, truth, name + " transposed")
+    for _ in range(3):  # bit-wise reproducible (reference: test/spmv/arch22/spmv_test.cpp:1184)
+        case.d_y.copy_(torch.from_numpy(y))
+        again = case.run(1.5, 0.5, preprocess=False)
+        assert np.array_equal(again.view(np.uint32), got.view(np.uint32))
+    # new values through the same plan: the permutation is applied at every product
+    va2 = (cfg["values"] * 0.5 + 1.0).astype(np.float32)
+    case.d_va.copy_(torch.from_numpy(va2))
+    case.d_y.copy_(torch.from_numpy(y))
+    got = case.run(1.5, 0.5, preprocess=False)
+    assert_close(got, O.spmv_transpose_f64(cfg["row_ptr"], cfg["col_ind"], va2, x, y, cfg["cols"], 1.5, 0.5),
+                 name + " transposed, new values")
+
+
+def test_transposed_long_columns():
+    """Columns with far more than 32 and than 2048 entries: every tier of the in-column sort."""
+    rng = np.random.default_rng(43)
+    rows, cols = 9000, 40
+    lengths = rng.integers(20, 40, rows)                     # every column gets about 6000 entries
+    rp, ci = random_csr(rng, lengths, cols)
+    va = rng.standard_normal(ci.size).astype(np.float32)
+    x = rng.standard_normal(rows).astype(np.float32)
+    y = np.zeros(cols, np.float32)
+    got = _transposed_case(rp, ci, va, x, y, cols).run(1.0, 0.0)
+    assert_close(got, O.spmv_transpose_f64(rp, ci, va, x, y, cols, 1.0, 0.0), "long columns")

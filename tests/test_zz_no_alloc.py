@@ -24,19 +24,31 @@ from tests.gpu_util import SpmvCase, dev  # noqa: E402
 RTOL, ATOL = 1e-5, 1e-6
 
 
-def _no_alloc(cfg, alpha, beta, base=0):
-    d_rp, d_ci, d_va = dev(cfg["row_ptr"] + base), dev(cfg["col_ind"] + base), dev(cfg["values"])
-    d_x, d_y = dev(cfg["x"]), dev(cfg["y"])
-    torch.cuda.synchronize()
-    before = torch.cuda.memory_allocated()
+def _call(cfg, arrays, alpha, beta, base):
+    d_rp, d_ci, d_va, d_x, d_y = arrays
     st = L.lib().aclsparseB200SpMVNoAlloc(
         c_void_p(torch.cuda.current_stream().cuda_stream or 0x1), cfg["rows"], cfg["cols"], cfg["nnz"],
         c_void_p(d_rp.data_ptr()), c_void_p(d_ci.data_ptr()), c_void_p(d_va.data_ptr()), base,
         c_void_p(d_x.data_ptr()), c_void_p(d_y.data_ptr()), alpha, beta)
     assert st == L.SUCCESS, L.STATUS_NAMES.get(st, st)
     torch.cuda.synchronize()
-    assert torch.cuda.memory_allocated() == before
-    return d_y.cpu().numpy()
+
+
+def _no_alloc(cfg, alpha, beta, base=0):
+    """One product through the entry point.  The first call on a device may load the library's device code and
+    look up the scratch (that can take device memory once); after a warm-up call the free device memory the
+    driver reports (cudaMemGetInfo, which sees every allocation, not only PyTorch's) must not move."""
+    arrays = (dev(cfg["row_ptr"] + base), dev(cfg["col_ind"] + base), dev(cfg["values"]), dev(cfg["x"]), dev(cfg["y"]))
+    _call(cfg, arrays, alpha, beta, base)                       # warm-up: result discarded below
+    arrays[4].copy_(torch.from_numpy(cfg["y"]))
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    reserved_before = torch.cuda.memory_reserved()
+    _call(cfg, arrays, alpha, beta, base)
+    free_after, _ = torch.cuda.mem_get_info()
+    assert torch.cuda.memory_reserved() == reserved_before     # PyTorch itself took nothing in between
+    assert free_after == free_before, f"device memory moved by {free_before - free_after} bytes during the call"
+    return arrays[4].cpu().numpy()
 
 
 def test_matches_the_buffered_entry_point_twice_in_a_row():
