@@ -319,6 +319,51 @@ aclsparseStatus_t aclsparseSpMM(aclsparseHandle_t handle, aclsparseOperation_t o
                                 const void* beta, aclsparseDnMatDescr_t matC, aclDataType computeType,
                                 aclsparseSpMMAlg_t alg, void* buffer);
 
+/* --------------------------------------------------- format producers -- */
+
+/* What feeds the path for callers that start from COO or from unsorted CSR: row offsets from sorted COO
+ * row indices, and the in-row sort of CSR column indices (with the permutation to apply to the values).
+ * Integer work, asynchronous on the handle's stream. */
+
+/* reference: include/cann_ops_sparse.h:225-241 */
+struct aclsparseMatDescr;
+typedef struct aclsparseMatDescr* aclsparseMatDescr_t;
+typedef enum aclsparseMatrixType_t {
+    ACL_SPARSE_MATRIX_TYPE_GENERAL = 0,
+    ACL_SPARSE_MATRIX_TYPE_SYMMETRIC,
+    ACL_SPARSE_MATRIX_TYPE_HERMITIAN,
+    ACL_SPARSE_MATRIX_TYPE_TRIANGULAR
+} aclsparseMatrixType_t;
+typedef enum aclsparseDiagType_t { ACL_SPARSE_DIAG_TYPE_NON_UNIT = 0, ACL_SPARSE_DIAG_TYPE_UNIT } aclsparseDiagType_t;
+typedef enum aclsparseFillMode_t { ACL_SPARSE_FILL_MODE_LOWER = 0, ACL_SPARSE_FILL_MODE_UPPER } aclsparseFillMode_t;
+
+/* reference: include/cann_ops_sparse.h:1659-1673; Destroy(NULL) is SUCCESS; the setters ignore NULL */
+aclsparseStatus_t aclsparseCreateMatDescr(aclsparseMatDescr_t* descr);
+aclsparseStatus_t aclsparseDestroyMatDescr(aclsparseMatDescr_t descr);
+void aclsparseSetMatType(aclsparseMatDescr_t descr, aclsparseMatrixType_t type);
+void aclsparseSetMatIndexBase(aclsparseMatDescr_t descr, aclsparseIndexBase_t base);
+void aclsparseSetMatDiagType(aclsparseMatDescr_t descr, aclsparseDiagType_t diagType);
+void aclsparseSetMatFillMode(aclsparseMatDescr_t descr, aclsparseFillMode_t fillMode);
+aclsparseMatrixType_t aclsparseGetMatType(aclsparseMatDescr_t descr);
+aclsparseIndexBase_t aclsparseGetMatIndexBase(aclsparseMatDescr_t descr);
+aclsparseDiagType_t aclsparseGetMatDiagType(aclsparseMatDescr_t descr);
+aclsparseFillMode_t aclsparseGetMatFillMode(aclsparseMatDescr_t descr);
+
+/* csrRowPtr[r] = idxBase + number of entries whose row is below r, r = 0..m, for COO row indices sorted
+ * non-decreasing (with idxBase).  reference: include/cann_ops_sparse.h:2800
+ * (sparse/coo2csr/arch35/coo2csr_host.cpp:38-77) */
+aclsparseStatus_t aclsparseXcoo2csr(aclsparseHandle_t handle, const int* cooRowInd, int nnz, int m, int* csrRowPtr,
+                                    aclsparseIndexBase_t idxBase);
+
+/* Sorts the column indices of every CSR row ascending, in place and stably, and applies the same
+ * permutation to P (the caller usually starts from the identity and gathers the values through P).
+ * The workspace holds 8 bytes per non-zero.  reference: include/cann_ops_sparse.h:2528,2545
+ * (sparse/csrsort/arch35/csrsort_host.cpp:40-215) */
+aclsparseStatus_t aclsparseXcsrsort_bufferSizeExt(aclsparseHandle_t handle, int m, int n, int nnz, const int* csrRowPtr,
+                                                  const int* csrColInd, size_t* pBufferSizeInBytes);
+aclsparseStatus_t aclsparseXcsrsort(aclsparseHandle_t handle, int m, int n, int nnz, const aclsparseMatDescr_t descrA,
+                                    const int* csrRowPtr, int* csrColInd, int* P, void* pBuffer);
+
 /* ------------------------------------------------------- SpMVOp / SpMMOp -- */
 
 /* The plan API: create once, execute many.

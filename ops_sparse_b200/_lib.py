@@ -131,6 +131,19 @@ SIGNATURES = {
     "aclsparseSpMMGetBufferSize": [_P, c_int, c_int, _P, _P, _P, _P, _P, c_int, c_int, POINTER(c_size_t)],
     "aclsparseSpMMPreprocess": [_P, c_int, c_int, _P, _P, _P, _P, _P, c_int, c_int, _P],
     "aclsparseSpMM": [_P, c_int, c_int, _P, _P, _P, _P, _P, c_int, c_int, _P],
+    "aclsparseCreateMatDescr": [_PP],
+    "aclsparseDestroyMatDescr": [_P],
+    "aclsparseSetMatType": [_P, c_int],
+    "aclsparseSetMatIndexBase": [_P, c_int],
+    "aclsparseSetMatDiagType": [_P, c_int],
+    "aclsparseSetMatFillMode": [_P, c_int],
+    "aclsparseGetMatType": [_P],
+    "aclsparseGetMatIndexBase": [_P],
+    "aclsparseGetMatDiagType": [_P],
+    "aclsparseGetMatFillMode": [_P],
+    "aclsparseXcoo2csr": [_P, _P, c_int, c_int, _P, c_int],
+    "aclsparseXcsrsort_bufferSizeExt": [_P, c_int, c_int, c_int, _P, _P, POINTER(c_size_t)],
+    "aclsparseXcsrsort": [_P, c_int, c_int, c_int, _P, _P, _P, _P, _P],
     "aclsparseSpMVOp_bufferSize": [_P, c_int, _P, _P, _P, _P, c_int, c_int, POINTER(c_size_t)],
     "aclsparseSpMVOp_createDescr": [_P, _PP, c_int, _P, _P, _P, _P, c_int, c_int, _P],
     "aclsparseSpMVOp_destroyDescr": [_P],
@@ -169,7 +182,8 @@ SIGNATURES = {
 _VOID = {"spmv_b200_preprocess_kernel_do", "spmv_b200_kernel_do", "spmm_b200_preprocess_kernel_do",
          "spmm_b200_kernel_do", "aclsp_b200_row_block_bounds_kernel_do", "aclsp_b200_push_slice_kernel_do",
          "aclsp_b200_node_barrier_kernel_do", "aclsp_b200_transpose_build_kernel_do",
-         "aclsp_b200_transpose_values_kernel_do"}
+         "aclsp_b200_transpose_values_kernel_do", "aclsparseSetMatType", "aclsparseSetMatIndexBase",
+         "aclsparseSetMatDiagType", "aclsparseSetMatFillMode"}
 
 _lib = None
 

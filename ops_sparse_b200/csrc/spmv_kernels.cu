@@ -37,9 +37,10 @@
  *   2. rows that end inside the tile are reduced by groups of 2^class lanes
  *      ("vector per row", class picked per tile by the preprocessing pass from
  *      the tile's mean row length; class 5 is warp per row) with a shuffle
- *      tree; pieces of kWarpSegment products or more that are too long for their
- *      lanes get a whole warp each (warp per row), pieces of kLongSegment or
- *      more the whole CTA;
+ *      tree; a piece that would keep its lanes busy for kLaneBudget products each
+ *      or more is set aside (the lanes of a warp run as long as the longest piece
+ *      among them) and gets eight lanes, a whole warp, or, from kLongSegment
+ *      products on, the whole CTA;
  *   3. the piece of a row that continues into the next tile becomes the tile's
  *      carry-out, and the piece of a row that began in an earlier tile becomes
  *      its head partial; a second small kernel adds the carries of a split row
@@ -79,7 +80,10 @@ namespace {
 constexpr int kThreads = 256;
 constexpr int kWarps = kThreads / 32;
 constexpr int kTile = ACLSP_SPMV_TILE_ITEMS;
-constexpr int kWarpSegment = 64;    // pieces at least this long get a whole warp
+constexpr int kLaneBudget = 16;     // a piece stays with its lanes while each of them adds fewer products than this
+constexpr int kOctetMax = 128;      // overflowing pieces shorter than this get eight lanes, longer ones a warp
+constexpr int kMaxOctetSeg = kTile / kLaneBudget;
+constexpr int kWarpSegment = 64;    // (capacity of the warp list: pieces on it are at least this long)
 constexpr int kLongSegment = 1024;  // pieces at least this long get the whole CTA
 constexpr int kMaxWarpSeg = kTile / kWarpSegment;
 constexpr int kMaxLong = kTile / kLongSegment;
@@ -222,6 +226,8 @@ struct ReduceScratch {
     double warp[kWarps];
     int longSeg[kMaxLong];
     int warpSeg[kMaxWarpSeg];
+    int octetSeg[kMaxOctetSeg];
+    int numOctetSeg;
     int numLong;
     int numWarpSeg;
 };
@@ -266,6 +272,8 @@ __device__ __forceinline__ void ReduceTile(const StagedTile& st, float* __restri
     int* sWarpSeg = scratch.warpSeg;
     int& sNumLong = scratch.numLong;
     int& sNumWarpSeg = scratch.numWarpSeg;
+    int* sOctetSeg = scratch.octetSeg;
+    int& sNumOctetSeg = scratch.numOctetSeg;
     (void)i1;
 
     const Scalars sc = LoadScalars(p);
@@ -337,20 +345,26 @@ __device__ __forceinline__ void ReduceTile(const StagedTile& st, float* __restri
             const int b = segBegin(k);
             const int e = segEnd(k);
             const int len = e - b;
-            if (len >= kWarpSegment && len >= 32 * lanes) {
-                // Too long for its lanes: queue it for a warp, or for the whole CTA.
-                // A valid CSR fills neither list beyond its capacity; row offsets
-                // that overlap could, and the excess is dropped.
+            if (len >= kLaneBudget * lanes) {
+                // Too long for its lanes (the lanes of a warp run as long as the longest piece among
+                // them, so one long piece would idle the others): queue it for eight lanes, for a
+                // warp, or for the whole CTA.  A valid CSR fills no list beyond its capacity; row
+                // offsets that overlap could, and the excess is dropped.
                 if (lane == 0) {
                     if (len >= kLongSegment) {
                         const int slot = atomicAdd(&sNumLong, 1);
                         if (slot < kMaxLong) {
                             sLong[slot] = k;
                         }
-                    } else {
+                    } else if (len >= kOctetMax || lanes >= 8) {
                         const int slot = atomicAdd(&sNumWarpSeg, 1);
                         if (slot < kMaxWarpSeg) {
                             sWarpSeg[slot] = k;
+                        }
+                    } else {
+                        const int slot = atomicAdd(&sNumOctetSeg, 1);
+                        if (slot < kMaxOctetSeg) {
+                            sOctetSeg[slot] = k;
                         }
                     }
                 }
@@ -368,6 +382,21 @@ __device__ __forceinline__ void ReduceTile(const StagedTile& st, float* __restri
         }
     }
     __syncthreads();
+
+    // Pieces a little too long for their lanes: eight lanes per piece.
+    const int numOctetSeg = sNumOctetSeg < kMaxOctetSeg ? sNumOctetSeg : kMaxOctetSeg;
+    for (int q0 = 0; q0 < numOctetSeg; q0 += kThreads / 8) {
+        const int q = q0 + (tid >> 3);
+        const bool has = q < numOctetSeg;
+        const int k = has ? sOctetSeg[q] : 0;
+        double sum = has ? strided(segBegin(k), segEnd(k), tid & 7, 8) : 0.0;
+        for (int o = 4; o > 0; o >>= 1) {
+            sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        }
+        if (has && (tid & 7) == 0) {
+            emit(k, sum);
+        }
+    }
 
     // Medium pieces: warp per row.
     const int numWarpSeg = sNumWarpSeg < kMaxWarpSeg ? sNumWarpSeg : kMaxWarpSeg;
@@ -497,6 +526,7 @@ SpmvTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ val
     if (tid == 0) {
         scratch.numLong = 0;
         scratch.numWarpSeg = 0;
+        scratch.numOctetSeg = 0;
     }
     for (int k = tid; k <= nr; k += kThreads) {
         sOff[k] = ClampOffset(plan.rowPtr[i0 + k], nnz) - j0;

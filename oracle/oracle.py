@@ -253,6 +253,28 @@ def transpose_twin(row_ptr, col_ind, cols: int, index_base=0):
     return row_ptr_t, row_of[perm].astype(np.int32), perm.astype(np.int32)
 
 
+def coo2csr_twin(coo_rows, m: int, index_base=0) -> np.ndarray:
+    """Row offsets of sorted COO row indices (twin of aclsparseXcoo2csr; reference semantics:
+    include/cann_ops_sparse.h:2783-2799, counting + prefix sum)."""
+    rows = np.asarray(coo_rows, dtype=np.int64) - index_base
+    return (np.searchsorted(rows, np.arange(m + 1), side="left") + index_base).astype(np.int32)
+
+
+def csrsort_twin(row_ptr, col_ind, perm, index_base=0):
+    """Stable in-row sort of CSR column indices and the same permutation applied to perm (twin of
+    aclsparseXcsrsort; reference semantics: include/cann_ops_sparse.h:2531-2544)."""
+    rp = np.asarray(row_ptr, dtype=np.int64) - index_base
+    col = np.array(col_ind, dtype=np.int32, copy=True)
+    out = np.array(perm, dtype=np.int32, copy=True)
+    for r in range(rp.size - 1):
+        b, e = int(rp[r]), int(rp[r + 1])
+        if e - b > 1:
+            order = np.argsort(col[b:e], kind="stable")
+            col[b:e] = col[b:e][order]
+            out[b:e] = out[b:e][order]
+    return col, out
+
+
 def row_block_bounds(row_ptr, nnz: int, parts: int, index_base=0) -> np.ndarray:
     row_ptr = _i32(row_ptr)
     bounds = np.empty(parts + 1, dtype=np.int32)

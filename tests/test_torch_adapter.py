@@ -60,9 +60,16 @@ def test_array_entry_checks_on_device_tensors():
     out = TA.spmv_csr(rp, ci, va, x, y, alpha=2.0, beta=0.0)
     torch.cuda.synchronize()
     assert out.data_ptr() == y.data_ptr() and y.tolist() == [2.0, 2.0]
-    from ops_sparse_b200 import api
-    with pytest.raises(api.AclsparseError):  # transpose is answered by the library, not by the adapter
-        TA.spmv_csr(rp, ci, va, x, y, trans="T")
+    # transposed products go through the same entry (the adapter passes op(A) on to the library)
+    rp3 = torch.tensor([0, 2, 3], dtype=torch.int32, device=dev)   # the reference's 2 x 3 fixture
+    ci3 = torch.tensor([0, 2, 1], dtype=torch.int32, device=dev)
+    va3 = torch.tensor([2.0, 3.0, 4.0], device=dev)
+    xt, yt = torch.tensor([1.0, 2.0], device=dev), torch.ones(3, device=dev)
+    for trans in ("T", "H"):
+        yt.fill_(1.0)
+        TA.spmv_csr(rp3, ci3, va3, xt, yt, alpha=2.0, beta=3.0, trans=trans)
+        torch.cuda.synchronize()
+        assert yt.tolist() == [7.0, 19.0, 9.0]
 
 
 @pytest.mark.gpu
