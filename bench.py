@@ -8,7 +8,8 @@ equivalent) with A resident on the device(s).  The headline workload is c2, the 
 160^3 grid (4 096 000 rows, 109 215 352 non-zeros), the configuration the headline metric is quoted
 on.  The same run then measures the other configurations of ops_sparse_b200/workloads.py (c1, c3, c4,
 c5 at one GPU; c3 and c4 at several) the same way and reports them under "configs" in the same line;
---configs picks another list, --configs none skips them.
+--configs picks another list, --configs none skips them.  At one GPU "configs" also holds the headline
+workload with its values and x stored as fp16 (fp32 result), "<workload>_fp16".
 
 At N GPUs (launched by torchrun, one rank per GPU) the same matrix is row-block sharded by nnz, x / B
 is replicated and every step ends with the reassembly of y / C on every rank, so total work is fixed
@@ -498,6 +499,62 @@ def measure(ctx: Context, args, cfg: dict, steps: int, warmup: int, min_warm_sec
     return result
 
 
+def measure_narrow(ctx: Context, args, cfg: dict, kind: str, steps: int, warmup: int) -> dict:
+    """SpMV of `cfg` with its values and x stored as fp16 or bf16 and an fp32 result, one GPU, through the C ABI:
+    device-resident steps timed with CUDA events, the whole result checked against the fp64 truth of the rounded
+    data.  Algorithmic bytes: 6 per non-zero instead of 8, 2 per element of x."""
+    from oracle import oracle as O
+    from ops_sparse_b200 import api
+    torch = ctx.torch
+    dev = ctx.device
+    dtype = torch.float16 if kind == "fp16" else torch.bfloat16
+    alpha, beta = cfg["alpha"], cfg["beta"]
+    va = torch.from_numpy(cfg["values"]).to(dev).to(dtype)
+    x = torch.from_numpy(cfg["x"]).to(dev).to(dtype)
+    rp = torch.from_numpy(cfg["row_ptr"]).to(dev)
+    ci = torch.from_numpy(cfg["col_ind"]).to(dev)
+    y0 = torch.from_numpy(cfg["y"]).to(dev)
+    y = y0.clone()
+    handle = api.Handle()
+    mat = api.CsrMatrix(cfg["rows"], cfg["cols"], rp, ci, va)
+    op = api.SpMV(handle, mat, api.DnVec(x), api.DnVec(y))
+    op.preprocess(alpha, beta)
+    op(alpha, beta)
+    torch.cuda.synchronize()
+    threads = host_threads()
+    truth = O.spmv_f64(cfg["row_ptr"], cfg["col_ind"], va.float().cpu().numpy(), x.float().cpu().numpy(), cfg["y"],
+                       alpha, beta, threads=threads)
+    bad, max_abs, max_rel = O.check_tolerance(y.cpu().numpy(), truth)
+    for _ in range(warmup):
+        y.copy_(y0)
+        op(alpha, beta)
+    torch.cuda.synchronize()
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+    ends = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+    launches0 = api.kernel_launches()
+    for i in range(steps):
+        y.copy_(y0)
+        starts[i].record()
+        op(alpha, beta)
+        ends[i].record()
+    torch.cuda.synchronize()
+    launches = api.kernel_launches() - launches0
+    ms = float(np.mean([s.elapsed_time(e) for s, e in zip(starts, ends)]))
+    m, nnz = cfg["rows"], cfg["nnz"]
+    abytes = nnz * 6 + (m + 1) * 4 + cfg["cols"] * 2 + m * 4 * (2 if beta != 0.0 else 1)
+    peak, peak_kind = measured_peak()
+    achieved = abytes / (ms * 1e-3) / 1e9
+    return {"metric": "spmv_gflops", "value": workloads.flops(cfg) / (ms * 1e-3) / 1e9, "unit": "GFLOP/s",
+            "ms_per_step": ms, "steps": steps, "warmup": warmup, "dtype": f"{kind} data, f64 accumulate, f32 result",
+            "config": {"workload": describe(cfg) + f", values and x rounded to {kind}", "launch": "kernel by kernel"},
+            "gpu_launches": int(launches),
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": None, "peak_kind": peak_kind, "algorithmic_bytes_per_launch": abytes,
+                         "kernel_ms": ms, "kernels": ["SpmvTileKernel<vector, narrow>", "SpmvCarryFixupKernel"]},
+            "check": {"rows_checked": m, "violations": int(bad), "ranks_checked": 1, "max_abs_err": max_abs,
+                      "max_rel_err": max_rel, "rtol": 1e-5, "atol": 1e-6}}
+
+
 def run_ours(args):
     ctx = Context(args)
     rank, world = ctx.rank, ctx.world
@@ -507,6 +564,9 @@ def run_ours(args):
     cfg = make_workload(ctx, args.workload, args.rows)
     head = measure(ctx, args, cfg, args.steps, args.warmup, 1.5)
     clocks = sampler.stop() if rank == 0 else None
+    narrow = None
+    if world == 1 and cfg["kind"] == "spmv" and not args.no_narrow:
+        narrow = measure_narrow(ctx, args, cfg, "fp16", args.steps, max(3, args.warmup))
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
@@ -532,6 +592,8 @@ def run_ours(args):
         del other
         gc.collect()
 
+    if narrow is not None:
+        configs[f"{args.workload}_fp16"] = narrow
     cleanup_shared(ctx)
     if world > 1:
         ctx.dist.barrier()  # last collective: every rank reaches it before any rank leaves
@@ -572,6 +634,7 @@ def main():
                     "replaying the step as one CUDA graph")
     ap.add_argument("--no-check", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-narrow", action="store_true", help="skip the fp16-storage variant of the headline workload")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.configs is not None:

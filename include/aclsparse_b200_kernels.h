@@ -62,9 +62,28 @@ typedef struct AclspSpmvParams {
      * element i at betaSource[i * betaSourceStride].  NULL: y is updated in place. */
     const float* betaSource;
     int64_t betaSourceStride;
+    /* Element types (ACLSP_TYPE_*).  valueType is the type of the matrix values and of x (the reference
+     * requires them equal, sparse/spmv/arch35/spmv_host.cpp:44-66), yType that of y and of betaSource.
+     * Zero-filled parameters mean fp32 throughout.  With valueType != ACLSP_TYPE_F32 the pointer
+     * arguments of the launcher address elements of these types, there are no mirrors, and
+     * - computeInt == 0: alpha / beta are the floats above, sums are fp64, y is rounded once, to nearest even;
+     * - computeInt == 1 (int8 values, int32 y): alphaInt / betaInt (device pointer mode: alphaPtr / betaPtr
+     *   address int32), the sum is exact and y = alpha*sum + beta*y saturates to the int32 range
+     *   (sparse/spmv/arch35/spmv_kernel.cpp:333-375). */
+    uint32_t valueType;
+    uint32_t yType;
+    uint32_t computeInt;
+    int32_t alphaInt;
+    int32_t betaInt;
 } AclspSpmvParams;
 
 #define ACLSP_MAX_ROW_LEN_UNKNOWN 0xFFFFFFFFu
+
+#define ACLSP_TYPE_F32 0u
+#define ACLSP_TYPE_F16 1u
+#define ACLSP_TYPE_BF16 2u
+#define ACLSP_TYPE_I8 3u
+#define ACLSP_TYPE_I32 4u
 
 /* Per-launch parameters of the SpMM kernels.  Counterpart of the reference's
  * SpmmTilingWireV1 (sparse/spmm/arch35/spmm_tiling_wire.h:23-74). */
@@ -88,6 +107,14 @@ typedef struct AclspSpmmParams {
     uint32_t numMirrors;     /* 0: C only */
     uint32_t mirrorMulticast;
     int64_t mirrorDelta[ACLSP_MAX_MIRRORS];
+    /* Element types (ACLSP_TYPE_*): valueType of the matrix values and of B (equal in every supported
+     * combination, sparse/spmm/arch35/host/spmm_host.cpp:379-387), cType of C; computeInt, alphaInt and
+     * betaInt as in AclspSpmvParams.  Zero-filled: fp32 throughout.  Narrow types: no mirrors. */
+    uint32_t valueType;
+    uint32_t cType;
+    uint32_t computeInt;
+    int32_t alphaInt;
+    int32_t betaInt;
 } AclspSpmmParams;
 
 /* Builds the SpMV plan in `workspace`: header, base-0 row offsets, merge-path
@@ -143,11 +170,11 @@ void aclsp_b200_transpose_build_kernel_do(const void* rowPtr, const void* colInd
                                           const struct AclspTransposeLayout* layout, void* stream);
 
 /* valuesT[p] = values[perm[p] * valuesStride] into the workspace of a transpose built by the call above
- * (the per-product part of op(A) = transpose).  Replaces spmm_transpose_values_launch
- * (reference: sparse/spmm/arch35/kernel/spmm_kernel_transpose.cpp:62). */
+ * (the per-product part of op(A) = transpose); elements of elemBytes (1, 2 or 4) bytes.  Replaces
+ * spmm_transpose_values_launch (reference: sparse/spmm/arch35/kernel/spmm_kernel_transpose.cpp:62). */
 void aclsp_b200_transpose_values_kernel_do(const void* values, int64_t valuesStride, uint32_t cols, uint32_t nnz,
                                            void* workspace, const struct AclspTransposeLayout* layout,
-                                           void* stream);
+                                           uint32_t elemBytes, void* stream);
 
 /* Number of kernels this library has launched in this process so far (all entry points, all streams;
  * launches recorded into a CUDA graph count once, at capture).  A diagnostic for benchmarks. */

@@ -59,7 +59,13 @@ class SpmvParams(ctypes.Structure):
                 ("colIndStride", c_int64), ("valuesStride", c_int64), ("xStride", c_int64), ("yStride", c_int64),
                 ("alpha", c_float), ("beta", c_float), ("alphaPtr", c_void_p), ("betaPtr", c_void_p),
                 ("numMirrors", c_uint32), ("mirrorMulticast", c_uint32), ("mirrorDelta", c_int64 * 7),
-                ("maxRowLenHint", c_uint32), ("betaSource", c_void_p), ("betaSourceStride", c_int64)]
+                ("maxRowLenHint", c_uint32), ("betaSource", c_void_p), ("betaSourceStride", c_int64),
+                ("valueType", c_uint32), ("yType", c_uint32), ("computeInt", c_uint32),
+                ("alphaInt", ctypes.c_int32), ("betaInt", ctypes.c_int32)]
+
+
+# SpmvParams.valueType / yType
+TYPE_F32, TYPE_F16, TYPE_BF16, TYPE_I8, TYPE_I32 = 0, 1, 2, 3, 4
 
 
 MAX_ROW_LEN_UNKNOWN = 0xFFFFFFFF  # SpmvParams.maxRowLenHint when the host does not know the longest row
@@ -71,7 +77,9 @@ class SpmmParams(ctypes.Structure):
                 ("n", c_uint32), ("opB", c_uint32), ("orderB", c_uint32), ("orderC", c_uint32),
                 ("highPrecision", c_uint32), ("reserved", c_uint32), ("ldb", c_int64), ("ldc", c_int64), ("alpha", c_float), ("beta", c_float),
                 ("alphaPtr", c_void_p), ("betaPtr", c_void_p),
-                ("numMirrors", c_uint32), ("mirrorMulticast", c_uint32), ("mirrorDelta", c_int64 * 7)]
+                ("numMirrors", c_uint32), ("mirrorMulticast", c_uint32), ("mirrorDelta", c_int64 * 7),
+                ("valueType", c_uint32), ("cType", c_uint32), ("computeInt", c_uint32),
+                ("alphaInt", ctypes.c_int32), ("betaInt", ctypes.c_int32)]
 
 
 _P = c_void_p
@@ -177,7 +185,7 @@ SIGNATURES = {
     "aclsp_b200_node_barrier_kernel_do": [_P, POINTER(c_void_p), c_uint32, c_uint32, c_uint32, _P],
     "aclsp_b200_kernel_launches": [],
     "aclsp_b200_transpose_build_kernel_do": [_P, _P, c_uint32, c_uint32, c_uint32, c_int32, c_int64, c_int64, _P, _P, _P],
-    "aclsp_b200_transpose_values_kernel_do": [_P, c_int64, c_uint32, c_uint32, _P, _P, _P],
+    "aclsp_b200_transpose_values_kernel_do": [_P, c_int64, c_uint32, c_uint32, _P, _P, c_uint32, _P],
 }
 _VOID = {"spmv_b200_preprocess_kernel_do", "spmv_b200_kernel_do", "spmm_b200_preprocess_kernel_do",
          "spmm_b200_kernel_do", "aclsp_b200_row_block_bounds_kernel_do", "aclsp_b200_push_slice_kernel_do",

@@ -71,8 +71,19 @@ class Handle:
             pass
 
 
+def acl_type(tensor) -> int:
+    """aclDataType of a tensor's elements (the value types the library's dtype tables name)."""
+    table = {torch.float32: L.ACL_FLOAT, torch.float16: L.ACL_FLOAT16, torch.bfloat16: L.ACL_BF16,
+             torch.int8: L.ACL_INT8, torch.int32: L.ACL_INT32}
+    if tensor is None:  # unbound storage (an empty matrix, or values bound later): fp32 unless said otherwise
+        return L.ACL_FLOAT
+    if tensor.dtype not in table:
+        raise TypeError(f"no aclDataType for {tensor.dtype}")
+    return table[tensor.dtype]
+
+
 class CsrMatrix:
-    """CSR descriptor over three CUDA tensors (int32 row offsets / column indices, fp32 values)."""
+    """CSR descriptor over three CUDA tensors (int32 row offsets / column indices; fp32, fp16, bf16 or int8 values)."""
 
     def __init__(self, rows: int, cols: int, row_offsets, col_indices, values, index_base: int = L.BASE_ZERO,
                  nnz: "int | None" = None):
@@ -83,7 +94,7 @@ class CsrMatrix:
         self._d = c_void_p(None)
         check("aclsparseCreateCsr", L.lib().aclsparseCreateCsr(
             byref(self._d), rows, cols, self.nnz, _ptr(row_offsets), _ptr(col_indices), _ptr(values), L.INDEX_32I,
-            L.INDEX_32I, index_base, L.ACL_FLOAT))
+            L.INDEX_32I, index_base, acl_type(values)))
 
     @property
     def raw(self) -> c_void_p:
@@ -107,7 +118,7 @@ class DnVec:
         self.size = int(values.numel()) if size is None else size
         self._d = c_void_p(None)
         check("aclsparseCreateDnVec", L.lib().aclsparseCreateDnVec(byref(self._d), self.size, _ptr(values),
-                                                                  L.ACL_FLOAT))
+                                                                  acl_type(values)))
 
     @property
     def raw(self) -> c_void_p:
@@ -144,7 +155,7 @@ class DnMat:
         self.rows, self.cols, self.ld, self.values, self.order = rows, cols, ld, values, order
         self._d = c_void_p(None)
         check("aclsparseCreateDnMat", L.lib().aclsparseCreateDnMat(byref(self._d), rows, cols, ld, _ptr(values),
-                                                                  L.ACL_FLOAT, order))
+                                                                  acl_type(values), order))
 
     @property
     def raw(self) -> c_void_p:
@@ -176,11 +187,12 @@ class DnMat:
             pass
 
 
-def _scalars(alpha, beta):
-    """Host scalars as C floats, or device tensors passed through for DEVICE pointer mode."""
+def _scalars(alpha, beta, integer: bool = False):
+    """Host scalars as C floats (int32 for the integer compute type), or device tensors passed through for
+    DEVICE pointer mode."""
     if isinstance(alpha, torch.Tensor):
         return _ptr(alpha), _ptr(beta), None
-    a, b = c_float(alpha), c_float(beta)
+    a, b = (ctypes.c_int32(alpha), ctypes.c_int32(beta)) if integer else (c_float(alpha), c_float(beta))
     return ctypes.cast(byref(a), c_void_p), ctypes.cast(byref(b), c_void_p), (a, b)
 
 
@@ -191,12 +203,15 @@ class SpMV:
                  op: int = L.OP_N):
         self.handle, self.mat, self.x, self.y, self.alg, self.op = handle, mat, x, y, alg, op
         self.buffer = None
+        # int8 data with an int32 result computes in int32 (integer alpha / beta, saturating); all else in fp32.
+        self.integer = y.values.dtype == torch.int32
+        self.compute_type = L.ACL_INT32 if self.integer else L.ACL_FLOAT
 
     def buffer_size(self, alpha=1.0, beta=0.0) -> int:
-        pa, pb, _keep = _scalars(alpha, beta)
+        pa, pb, _keep = _scalars(alpha, beta, self.integer)
         size = c_size_t(0)
         check("aclsparseSpMVGetBufferSize", L.lib().aclsparseSpMVGetBufferSize(
-            self.handle.raw, self.op, pa, self.mat.raw, self.x.raw, pb, self.y.raw, L.ACL_FLOAT, self.alg,
+            self.handle.raw, self.op, pa, self.mat.raw, self.x.raw, pb, self.y.raw, self.compute_type, self.alg,
             byref(size)))
         return int(size.value)
 
@@ -208,17 +223,17 @@ class SpMV:
     def preprocess(self, alpha=1.0, beta=0.0) -> None:
         if self.buffer is None:
             self.allocate(alpha, beta)
-        pa, pb, _keep = _scalars(alpha, beta)
+        pa, pb, _keep = _scalars(alpha, beta, self.integer)
         check("aclsparseSpMVPreprocess", L.lib().aclsparseSpMVPreprocess(
-            self.handle.raw, self.op, pa, self.mat.raw, self.x.raw, pb, self.y.raw, L.ACL_FLOAT, self.alg,
+            self.handle.raw, self.op, pa, self.mat.raw, self.x.raw, pb, self.y.raw, self.compute_type, self.alg,
             _ptr(self.buffer)))
 
     def __call__(self, alpha=1.0, beta=0.0) -> None:
         if self.buffer is None:
             self.allocate(alpha, beta)
-        pa, pb, _keep = _scalars(alpha, beta)
+        pa, pb, _keep = _scalars(alpha, beta, self.integer)
         check("aclsparseSpMV", L.lib().aclsparseSpMV(
-            self.handle.raw, self.op, pa, self.mat.raw, self.x.raw, pb, self.y.raw, L.ACL_FLOAT, self.alg,
+            self.handle.raw, self.op, pa, self.mat.raw, self.x.raw, pb, self.y.raw, self.compute_type, self.alg,
             _ptr(self.buffer)))
 
 
@@ -229,12 +244,15 @@ class SpMM:
                  op_a: int = L.OP_N, op_b: int = L.OP_N):
         self.handle, self.mat, self.b, self.c, self.alg, self.op_a, self.op_b = handle, mat, b, c, alg, op_a, op_b
         self.buffer = None
+        # int8 data with an int32 result computes in int32 (integer alpha / beta, saturating); all else in fp32.
+        self.integer = c.values.dtype == torch.int32
+        self.compute_type = L.ACL_INT32 if self.integer else L.ACL_FLOAT
 
     def buffer_size(self, alpha=1.0, beta=0.0) -> int:
-        pa, pb, _keep = _scalars(alpha, beta)
+        pa, pb, _keep = _scalars(alpha, beta, self.integer)
         size = c_size_t(0)
         check("aclsparseSpMMGetBufferSize", L.lib().aclsparseSpMMGetBufferSize(
-            self.handle.raw, self.op_a, self.op_b, pa, self.mat.raw, self.b.raw, pb, self.c.raw, L.ACL_FLOAT,
+            self.handle.raw, self.op_a, self.op_b, pa, self.mat.raw, self.b.raw, pb, self.c.raw, self.compute_type,
             self.alg, byref(size)))
         return int(size.value)
 
@@ -246,18 +264,23 @@ class SpMM:
     def preprocess(self, alpha=1.0, beta=0.0) -> None:
         if self.buffer is None:
             self.allocate(alpha, beta)
-        pa, pb, _keep = _scalars(alpha, beta)
+        pa, pb, _keep = _scalars(alpha, beta, self.integer)
         check("aclsparseSpMMPreprocess", L.lib().aclsparseSpMMPreprocess(
-            self.handle.raw, self.op_a, self.op_b, pa, self.mat.raw, self.b.raw, pb, self.c.raw, L.ACL_FLOAT,
+            self.handle.raw, self.op_a, self.op_b, pa, self.mat.raw, self.b.raw, pb, self.c.raw, self.compute_type,
             self.alg, _ptr(self.buffer)))
 
     def __call__(self, alpha=1.0, beta=0.0) -> None:
         if self.buffer is None:
             self.allocate(alpha, beta)
-        pa, pb, _keep = _scalars(alpha, beta)
+        pa, pb, _keep = _scalars(alpha, beta, self.integer)
         check("aclsparseSpMM", L.lib().aclsparseSpMM(
-            self.handle.raw, self.op_a, self.op_b, pa, self.mat.raw, self.b.raw, pb, self.c.raw, L.ACL_FLOAT,
+            self.handle.raw, self.op_a, self.op_b, pa, self.mat.raw, self.b.raw, pb, self.c.raw, self.compute_type,
             self.alg, _ptr(self.buffer)))
+
+
+def kernel_launches() -> int:
+    """Kernels the library has launched in this process so far (aclsp_b200_kernel_launches)."""
+    return int(L.lib().aclsp_b200_kernel_launches())
 
 
 def row_block_bounds(handle: Handle, mat: CsrMatrix, parts: int) -> torch.Tensor:

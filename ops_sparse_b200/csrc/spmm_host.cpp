@@ -10,7 +10,8 @@
  *    the external buffer during preprocessing, on the device, and multiplies with it (the reference
  *    builds a CSC copy on the host, spmm_csr_mat.cpp:212-315); the buffer then needs about 12 bytes
  *    per non-zero more;
- *  - only fp32 A, B, C with an fp32 compute type is accepted;
+ *  - the complex row of the reference's dtype table (spmm_host.cpp:379-387) is answered with NOT_SUPPORTED;
+ *    the others (fp32, fp16 / bf16 A and B with C of the same type or fp32, int8 with an int32 C) are computed;
  *  - the buffer must be 64-byte aligned (INVALID_VALUE otherwise) and its size
  *    covers the B200 plan, not the reference's reorder table;
  *  - preprocessing never copies anything to the host, and the plan depends on
@@ -86,9 +87,24 @@ aclsparseStatus_t CheckInputs(const aclsparseSpMatDescr* a, const aclsparseDnMat
     if (a->nnz > static_cast<uint64_t>(kMaxI32)) {
         return ACL_SPARSE_STATUS_NOT_SUPPORTED;
     }
-    if (!(a->valueType == ACL_FLOAT && b->valueType == ACL_FLOAT && c->valueType == ACL_FLOAT &&
-          computeType == ACL_FLOAT)) {
-        ACLSP_LOGE(kApi, "unsupported data type combination A=%d B=%d C=%d compute=%d; fp32 only",
+    // The reference's table (sparse/spmm/arch35/host/spmm_host.cpp:379-387) without its complex row.
+    const aclDataType vt = a->valueType;
+    const aclDataType ct = c->valueType;
+    bool supported = vt == b->valueType;
+    if (computeType == ACL_INT32) {
+        supported = supported && vt == ACL_INT8 && ct == ACL_INT32;
+    } else if (computeType == ACL_FLOAT) {
+        supported = supported && ((vt == ACL_FLOAT && ct == ACL_FLOAT) ||
+                                  (vt == ACL_FLOAT16 && (ct == ACL_FLOAT16 || ct == ACL_FLOAT)) ||
+                                  (vt == ACL_BF16 && (ct == ACL_BF16 || ct == ACL_FLOAT)));
+    } else {
+        supported = false;
+    }
+    if (supported && vt != ACL_FLOAT && c->numMirrors != 0) {
+        supported = false;  // mirrors of C are for fp32 products
+    }
+    if (!supported) {
+        ACLSP_LOGE(kApi, "unsupported data type combination A=%d B=%d C=%d compute=%d",
                    static_cast<int>(a->valueType), static_cast<int>(b->valueType), static_cast<int>(c->valueType),
                    static_cast<int>(computeType));
         return ACL_SPARSE_STATUS_NOT_SUPPORTED;
@@ -329,7 +345,9 @@ extern "C" aclsparseStatus_t aclsparseSpMM(aclsparseHandle_t handle, aclsparseOp
         AclspTransposeLayout tl;
         (void)BufferLayout(a, n, true, &tl);
         aclsp_b200_transpose_values_kernel_do(a->values, 1, static_cast<uint32_t>(a->cols),
-                                              static_cast<uint32_t>(a->nnz), buffer, &tl, handle->stream);
+                                              static_cast<uint32_t>(a->nnz), buffer, &tl,
+                                              a->valueType == ACL_INT8 ? 1u : (a->valueType == ACL_FLOAT ? 4u : 2u),
+                                              handle->stream);
         colInd = static_cast<const unsigned char*>(buffer) + tl.colIndOff;
         values = static_cast<const unsigned char*>(buffer) + tl.valuesOff;
         params.rows = static_cast<uint32_t>(a->cols);
@@ -343,9 +361,22 @@ extern "C" aclsparseStatus_t aclsparseSpMM(aclsparseHandle_t handle, aclsparseOp
     params.highPrecision = alg == ACL_SPARSE_SPMM_CSR_FP32_HIGH_PRECISION_ALG ? 1u : 0u;
     params.ldb = matB->ld;
     params.ldc = matC->ld;
+    auto kernelType = [](aclDataType t) {
+        return t == ACL_FLOAT16 ? ACLSP_TYPE_F16
+               : t == ACL_BF16  ? ACLSP_TYPE_BF16
+               : t == ACL_INT8  ? ACLSP_TYPE_I8
+               : t == ACL_INT32 ? ACLSP_TYPE_I32
+                                : ACLSP_TYPE_F32;
+    };
+    params.valueType = kernelType(a->valueType);
+    params.cType = kernelType(matC->valueType);
+    params.computeInt = computeType == ACL_INT32 ? 1u : 0u;
     if (handle->pointerMode == ACL_SPARSE_POINTER_MODE_DEVICE) {
-        params.alphaPtr = static_cast<const float*>(alpha);
+        params.alphaPtr = static_cast<const float*>(alpha);  // int32 on the device when computeInt
         params.betaPtr = static_cast<const float*>(beta);
+    } else if (params.computeInt != 0) {
+        params.alphaInt = *static_cast<const int32_t*>(alpha);
+        params.betaInt = *static_cast<const int32_t*>(beta);
     } else {
         params.alpha = *static_cast<const float*>(alpha);
         params.beta = *static_cast<const float*>(beta);

@@ -46,6 +46,7 @@
 #include <cuda_runtime.h>
 
 #include "aclsparse_b200_kernels.h"
+#include "element_types.cuh"
 #include "plan_kernels.h"
 #include "plan_layout.h"
 
@@ -56,6 +57,9 @@ constexpr int kWarps = kThreads / 32;
 constexpr int kTile = ACLSP_SPMM_TILE_ITEMS;
 constexpr int kWarpItems = kTile / kWarps;
 constexpr int kStages = 8;
+
+using aclsp::kF32;
+using aclsp::LoadIn;
 
 struct SpmmPlanView {
     const int32_t* rowPtr;
@@ -181,11 +185,15 @@ constexpr size_t SmemBytes(int vw)
            + sizeof(int) * (2 * kWarps + 2);            // warp row split, head flags
 }
 
-template <int VW, bool kStageB>
+// kIn != kF32 (narrow storage: fp16, bf16 or int8 values and B, C of type p.cType): `values`, `B` and `C`
+// address elements of those types; only the one-column-per-lane form without staging exists (VW = 1,
+// kStageB = false), which goes through element strides and so covers every layout.
+template <int VW, bool kStageB, int kIn = kF32>
 __global__ void __launch_bounds__(kThreads)
 SpmmTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ values, const float* __restrict__ B,
                float* __restrict__ C, SpmmPlanView plan, AclspSpmmParams p, DenseStrides ds)
 {
+    static_assert(kIn == kF32 || (VW == 1 && !kStageB), "narrow storage: one column per lane, no staging");
     using V = typename Vec<VW>::T;
     constexpr int kPanel = 32 * VW;
 
@@ -230,7 +238,8 @@ SpmmTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ val
         sOff[k] = ClampOffset(plan.rowPtr[i0 + k], nnz) - j0;
     }
     {
-        const bool vector = (reinterpret_cast<uintptr_t>(colInd) | reinterpret_cast<uintptr_t>(values)) % 16 == 0;
+        const bool vector = kIn == kF32 &&
+                            (reinterpret_cast<uintptr_t>(colInd) | reinterpret_cast<uintptr_t>(values)) % 16 == 0;
         const int a0 = vector ? (j0 & ~3) : j0;
         const int count = j1 - a0;
         for (int e = 4 * tid; e < count; e += 4 * kThreads) {
@@ -247,7 +256,7 @@ SpmmTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ val
                 for (int q = 0; q < 4; ++q) {
                     const bool in = g + q < nnz;
                     c[q] = in ? __ldcs(colInd + g + q) : -1;
-                    w[q] = in ? __ldcs(values + g + q) : 0.0f;
+                    w[q] = in ? LoadIn<kIn>(values, g + q) : 0.0f;
                 }
             }
 #pragma unroll
@@ -284,6 +293,9 @@ SpmmTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ val
     }
 
     const Scalars sc = LoadScalars(p);
+    const aclsp::TypedScalars tsc = aclsp::LoadTypedScalars(p.computeInt, p.alphaPtr, p.betaPtr, p.alpha, p.beta,
+                                                            p.alphaInt, p.betaInt);
+    (void)tsc;
     float* ring = sRing + warp * kStages * kPanel + lane * VW;
     const bool tileHeadOpen = sOff[0] < 0;
 
@@ -313,6 +325,11 @@ SpmmTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ val
         // C[row] = alpha * sum + beta * C[row]; beta == 0 never reads C.
         auto storeRow = [&](int localRow, const double (&sum)[VW]) {
             if (!colOk) {
+                return;
+            }
+            if constexpr (kIn != kF32) {
+                const int64_t at = static_cast<int64_t>(colL) * ds.cCol + static_cast<int64_t>(i0 + localRow) * ds.cRow;
+                aclsp::StoreScaled(p.cType, C, at, C, at, sum[0], tsc);
                 return;
             }
             float* dst = cLane + static_cast<int64_t>(i0 + localRow) * ds.cRow;
@@ -412,7 +429,11 @@ SpmmTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ val
                     const int c = qq < q1 ? sCol[qq] : -1;
                     const bool ok = c >= 0 && colOk;
                     a[u] = ok ? sVal[qq] : 0.0f;
-                    if (ok) {
+                    if constexpr (kIn != kF32) {
+                        *reinterpret_cast<float*>(&b[u]) =
+                            ok ? LoadIn<kIn>(B, static_cast<int64_t>(colL) * ds.bCol + static_cast<int64_t>(c) * ds.bRow)
+                               : 0.0f;
+                    } else if (ok) {
                         b[u] = __ldg(reinterpret_cast<const V*>(bLane + static_cast<int64_t>(c) * ds.bRow));
                     } else {
                         float* z = reinterpret_cast<float*>(&b[u]);
@@ -497,6 +518,7 @@ SpmmTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ val
 // One warp per tile whose first row began in an earlier tile and ends in this
 // one: adds the tails of the tiles the row crossed, oldest first, then the head
 // piece, and writes the row of C.
+template <int kIn = kF32>
 __global__ void SpmmCarryFixupKernel(float* __restrict__ C, SpmmPlanView plan, AclspSpmmParams p, DenseStrides ds)
 {
     const int lane = threadIdx.x & 31;
@@ -526,6 +548,13 @@ __global__ void SpmmCarryFixupKernel(float* __restrict__ C, SpmmPlanView plan, A
                 sum += plan.carry[static_cast<size_t>(2 * u) * n + c];
             }
             sum += plan.carry[static_cast<size_t>(2 * t + 1) * n + c];
+            if constexpr (kIn != kF32) {
+                const int64_t at = static_cast<int64_t>(i0) * ds.cRow + static_cast<int64_t>(c) * ds.cCol;
+                aclsp::StoreScaled(p.cType, C, at, C, at, sum,
+                                   aclsp::LoadTypedScalars(p.computeInt, p.alphaPtr, p.betaPtr, p.alpha, p.beta,
+                                                           p.alphaInt, p.betaInt));
+                continue;
+            }
             float* dst = C + static_cast<int64_t>(i0) * ds.cRow + static_cast<int64_t>(c) * ds.cCol;
             const double r = static_cast<double>(sc.alpha) * sum;
             const float out = static_cast<float>(sc.betaZero ? r : r + static_cast<double>(sc.beta) * *dst);
@@ -574,6 +603,22 @@ void LaunchByPrecision(const void* colInd, const void* values, const void* b, vo
     }
 }
 
+template <int kIn>
+void LaunchNarrow(const void* colInd, const void* values, const void* b, void* c, const SpmmPlanView& plan,
+                  const AclspSpmmParams& p, const DenseStrides& ds, cudaStream_t s)
+{
+    constexpr size_t smem = SmemBytes(1);
+    cudaFuncSetAttribute(SpmmTileKernel<1, false, kIn>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         static_cast<int>(smem));
+    AclspCountLaunches(2);
+    SpmmTileKernel<1, false, kIn><<<plan.numTiles, kThreads, smem, s>>>(
+        static_cast<const int32_t*>(colInd), static_cast<const float*>(values), static_cast<const float*>(b),
+        static_cast<float*>(c), plan, p, ds);
+    uint32_t blocks = (plan.numTiles + 7u) / 8u;
+    blocks = blocks > 148u * 8u ? 148u * 8u : blocks;
+    SpmmCarryFixupKernel<kIn><<<blocks, 256, 0, s>>>(static_cast<float*>(c), plan, p, ds);
+}
+
 }  // namespace
 
 extern "C" void spmm_b200_kernel_do(const void* colInd, const void* values, const void* b, void* c,
@@ -593,6 +638,19 @@ extern "C" void spmm_b200_kernel_do(const void* colInd, const void* values, cons
     ds.cRow = p.orderC == 0 ? p.ldc : 1;
     ds.cCol = p.orderC == 0 ? 1 : p.ldc;
 
+    if (p.valueType != ACLSP_TYPE_F32) {
+        AclspSpmmParams q = p;
+        q.numMirrors = 0;
+        q.mirrorMulticast = 0;
+        if (p.valueType == ACLSP_TYPE_F16) {
+            LaunchNarrow<aclsp::kF16>(colInd, values, b, c, plan, q, ds, s);
+        } else if (p.valueType == ACLSP_TYPE_BF16) {
+            LaunchNarrow<aclsp::kBF16>(colInd, values, b, c, plan, q, ds, s);
+        } else if (p.valueType == ACLSP_TYPE_I8) {
+            LaunchNarrow<aclsp::kI8>(colInd, values, b, c, plan, q, ds, s);
+        }
+        return;
+    }
     const bool unit = ds.bCol == 1 && ds.cCol == 1;
     uintptr_t addr = reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(c);
     for (uint32_t m = 0; m < p.numMirrors && m < ACLSP_MAX_MIRRORS; ++m) {
@@ -614,5 +672,5 @@ extern "C" void spmm_b200_kernel_do(const void* colInd, const void* values, cons
     uint32_t blocks = (plan.numTiles + 7u) / 8u;
     blocks = blocks > 148u * 8u ? 148u * 8u : blocks;
     AclspCountLaunches(1);
-    SpmmCarryFixupKernel<<<blocks, 256, 0, s>>>(static_cast<float*>(c), plan, p, ds);
+    SpmmCarryFixupKernel<kF32><<<blocks, 256, 0, s>>>(static_cast<float*>(c), plan, p, ds);
 }

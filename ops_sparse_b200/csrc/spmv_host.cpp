@@ -10,8 +10,9 @@
  *  - op(A) = transpose (and conjugate transpose, the same thing for real data) builds the transposed
  *    matrix in the external buffer during preprocessing and multiplies with it: the buffer is much
  *    larger (about 12 bytes per non-zero) and the result is bit-reproducible for every algorithm value;
- *  - only fp32 A, x, y with an fp32 compute type is accepted (the reference's
- *    other dtype combinations are answered with NOT_SUPPORTED);
+ *  - the complex dtype combinations of the reference's table (spmv_host.cpp:44-66) are answered with
+ *    NOT_SUPPORTED; the others (fp32, fp16 / bf16 storage with a result of the same type or fp32, int8 with
+ *    an fp32 or a saturating int32 result) are computed;
  *  - the buffer size covers the B200 plan (row offsets + tile splits + row
  *    bins + carries), so it is larger than the reference's for the same matrix.
  */
@@ -55,6 +56,22 @@ size_t ScalarAlignment(aclDataType computeType)
             return alignof(float);
         default:
             return 0;
+    }
+}
+
+uint32_t KernelType(aclDataType t)
+{
+    switch (t) {
+        case ACL_FLOAT16:
+            return ACLSP_TYPE_F16;
+        case ACL_BF16:
+            return ACLSP_TYPE_BF16;
+        case ACL_INT8:
+            return ACLSP_TYPE_I8;
+        case ACL_INT32:
+            return ACLSP_TYPE_I32;
+        default:
+            return ACLSP_TYPE_F32;
     }
 }
 
@@ -150,12 +167,27 @@ aclsparseStatus_t CheckMatrix(const aclsparseSpMatDescr* mat, const aclsparseDnV
         return ACL_SPARSE_STATUS_NOT_SUPPORTED;
     }
     // Repeated coordinates are legal, so nnz is not bounded by rows*cols.
-    const bool fp32 = mat->valueType == ACL_FLOAT && x->valueType == ACL_FLOAT && y->valueType == ACL_FLOAT &&
-                      computeType == ACL_FLOAT;
-    if (!fp32) {
-        ACLSP_LOGE(kApi, "unsupported dtype combination A=%d x=%d y=%d compute=%d; fp32 only",
+    // The reference's table (sparse/spmv/arch35/spmv_host.cpp:44-66) without its complex rows.
+    const aclDataType vt = mat->valueType;
+    const aclDataType yt = y->valueType;
+    bool supported = vt == x->valueType;
+    if (computeType == ACL_INT32) {
+        supported = supported && vt == ACL_INT8 && yt == ACL_INT32;
+    } else if (computeType == ACL_FLOAT) {
+        supported = supported && ((vt == ACL_FLOAT && yt == ACL_FLOAT) || (vt == ACL_INT8 && yt == ACL_FLOAT) ||
+                                  (vt == ACL_FLOAT16 && (yt == ACL_FLOAT16 || yt == ACL_FLOAT)) ||
+                                  (vt == ACL_BF16 && (yt == ACL_BF16 || yt == ACL_FLOAT)));
+    } else {
+        supported = false;
+    }
+    if (!supported) {
+        ACLSP_LOGE(kApi, "unsupported dtype combination A=%d x=%d y=%d compute=%d",
                    static_cast<int>(mat->valueType), static_cast<int>(x->valueType),
                    static_cast<int>(y->valueType), static_cast<int>(computeType));
+        return ACL_SPARSE_STATUS_NOT_SUPPORTED;
+    }
+    if (vt != ACL_FLOAT && y->numMirrors != 0) {
+        ACLSP_LOGE(kApi, "mirrors of y are for fp32 products");
         return ACL_SPARSE_STATUS_NOT_SUPPORTED;
     }
     (void)opA;
@@ -446,7 +478,8 @@ extern "C" aclsparseStatus_t aclsparseSpMV(aclsparseHandle_t handle, aclsparseOp
         AclspTransposeLayout tl;
         (void)BufferLayout(mat, true, &tl);
         aclsp_b200_transpose_values_kernel_do(mat->values, mat->valueStride, static_cast<uint32_t>(mat->cols),
-                                              static_cast<uint32_t>(mat->nnz), externalBuffer, &tl, handle->stream);
+                                              static_cast<uint32_t>(mat->nnz), externalBuffer, &tl,
+                                              static_cast<uint32_t>(ElementBytes(mat->valueType)), handle->stream);
         colInd = static_cast<const unsigned char*>(externalBuffer) + tl.colIndOff;
         values = static_cast<const unsigned char*>(externalBuffer) + tl.valuesOff;
         params.rows = static_cast<uint32_t>(mat->cols);
@@ -457,10 +490,16 @@ extern "C" aclsparseStatus_t aclsparseSpMV(aclsparseHandle_t handle, aclsparseOp
     }
     params.xStride = vecX->stride;
     params.yStride = vecY->stride;
+    params.valueType = KernelType(mat->valueType);
+    params.yType = KernelType(vecY->valueType);
+    params.computeInt = computeType == ACL_INT32 ? 1u : 0u;
     if (handle->pointerMode == ACL_SPARSE_POINTER_MODE_DEVICE) {
-        // The host never dereferences device scalars; the kernels read them.
+        // The host never dereferences device scalars; the kernels read them (as int32 when computeInt).
         params.alphaPtr = static_cast<const float*>(alpha);
         params.betaPtr = static_cast<const float*>(beta);
+    } else if (params.computeInt != 0) {
+        params.alphaInt = *static_cast<const int32_t*>(alpha);
+        params.betaInt = *static_cast<const int32_t*>(beta);
     } else {
         params.alpha = *static_cast<const float*>(alpha);
         params.beta = *static_cast<const float*>(beta);

@@ -68,10 +68,12 @@
 #include <cstdint>
 
 #include <cstdlib>
+#include <type_traits>
 
 #include <cuda_runtime.h>
 
 #include "aclsparse_b200_kernels.h"
+#include "element_types.cuh"
 #include "plan_kernels.h"
 #include "plan_layout.h"
 
@@ -115,23 +117,23 @@ __device__ __forceinline__ int ClampOffset(int v, int nnz)
     return v < 0 ? 0 : (v > nnz ? nnz : v);
 }
 
+// Type of the matrix values and of x (template parameter kIn of the kernels): fp32 is the fast path
+// and the only one with row blocks and mirrors; the narrow types run the tile kernel.  Their products
+// are exact in fp32, so they need no error term; only a bf16 product can overflow, and then the sum is
+// recomputed in fp64 like any other non-finite sum.
+using aclsp::kBF16;
+using aclsp::kF16;
+using aclsp::kF32;
+using aclsp::kI8;
+using aclsp::LoadIn;
+
 /* ------------------------------------------------------------ product -- */
 
-struct Scalars {
-    double alpha;
-    double beta;
-    bool betaZero;
-};
+using Scalars = aclsp::TypedScalars;
 
 __device__ __forceinline__ Scalars LoadScalars(const AclspSpmvParams& p)
 {
-    const float a = p.alphaPtr != nullptr ? *p.alphaPtr : p.alpha;
-    const float b = p.betaPtr != nullptr ? *p.betaPtr : p.beta;
-    Scalars s;
-    s.alpha = static_cast<double>(a);
-    s.beta = static_cast<double>(b);
-    s.betaZero = b == 0.0f;
-    return s;
+    return aclsp::LoadTypedScalars(p.computeInt, p.alphaPtr, p.betaPtr, p.alpha, p.beta, p.alphaInt, p.betaInt);
 }
 
 // Row `row` of the result: alpha * sum + beta * (the vector beta scales), written to `at`.  The
@@ -148,6 +150,15 @@ __device__ __forceinline__ float StoreRow(float* at, int64_t row, double sum, co
     const float out = static_cast<float>(r);
     *at = out;
     return out;
+}
+
+// The same for an output of any element type (p.yType); y and p.betaSource address elements of that type.
+__device__ __forceinline__ void StoreRowTyped(void* y, int64_t row, double sum, const Scalars& s, const AclspSpmvParams& p)
+{
+    const int64_t at = row * p.yStride;
+    const void* from = p.betaSource != nullptr ? static_cast<const void*>(p.betaSource) : y;
+    const int64_t fromAt = p.betaSource != nullptr ? row * p.betaSourceStride : at;
+    aclsp::StoreScaled(p.yType, y, at, from, fromAt, sum, s);
 }
 
 // Mirrors of y (the other GPUs' result buffers when the matrix is sharded)
@@ -184,7 +195,8 @@ __device__ __forceinline__ void MirrorStore(float4* dst, const float4& v, const 
 // One product as an unevaluated sum hi + lo of two floats: hi is the rounded
 // fp32 product and lo its exact rounding error, so hi + lo == a * x[col]
 // exactly.  Entries whose column is out of range contribute nothing.
-__device__ __forceinline__ void Product(float a, int32_t rawCol, const float* __restrict__ x, uint32_t base,
+template <int kIn = kF32>
+__device__ __forceinline__ void Product(float a, int32_t rawCol, const void* __restrict__ x, uint32_t base,
                                         uint32_t cols, int64_t xStride, float& hi, float& lo)
 {
     const uint32_t c = static_cast<uint32_t>(rawCol) - base;
@@ -193,9 +205,9 @@ __device__ __forceinline__ void Product(float a, int32_t rawCol, const float* __
         lo = 0.0f;
         return;
     }
-    const float xv = __ldg(x + static_cast<int64_t>(c) * xStride);
+    const float xv = LoadIn<kIn>(x, static_cast<int64_t>(c) * xStride);
     hi = __fmul_rn(a, xv);
-    lo = fmaf(a, xv, -hi);
+    lo = kIn == kF32 ? fmaf(a, xv, -hi) : 0.0f;  // products of the narrow types are exact
 }
 
 __device__ __forceinline__ bool Finite(double v)
@@ -205,7 +217,8 @@ __device__ __forceinline__ bool Finite(double v)
 
 // Non-zeros [e0, e1) of the arrays multiplied and added in fp64, in array order.  Rare (only
 // for sums that came out non-finite), so it is kept out of line and takes everything by value.
-__device__ __forceinline__ double ExactSum(const int32_t* colInd, const float* values, const float* x, int64_t e0,
+template <int kIn = kF32>
+__device__ __forceinline__ double ExactSum(const int32_t* colInd, const void* values, const void* x, int64_t e0,
                                         int64_t e1, int64_t colIndStride, int64_t valuesStride, int64_t xStride,
                                         uint32_t indexBase, uint32_t cols)
 {
@@ -213,7 +226,8 @@ __device__ __forceinline__ double ExactSum(const int32_t* colInd, const float* v
     for (int64_t e = e0; e < e1; ++e) {
         const uint32_t col = static_cast<uint32_t>(colInd[e * colIndStride]) - indexBase;
         if (col < cols) {
-            s += static_cast<double>(values[e * valuesStride]) * static_cast<double>(x[static_cast<int64_t>(col) * xStride]);
+            s += static_cast<double>(LoadIn<kIn>(values, e * valuesStride)) *
+                 static_cast<double>(LoadIn<kIn>(x, static_cast<int64_t>(col) * xStride));
         }
     }
     return s;
@@ -236,8 +250,8 @@ struct ReduceScratch {
 // to the tile's first product, and nr spare words for the mirrors of y.
 struct StagedTile {
     const int32_t* colInd;  // the global arrays, for the exact recomputation of a non-finite piece
-    const float* values;
-    const float* x;
+    const void* values;
+    const void* x;
     int j0;                 // index of the tile's first product in them
     int t;
     int i0;
@@ -254,6 +268,7 @@ struct StagedTile {
 // Reduces the rows of a staged tile and writes them (y, mirrors, carries).
 // Called by all threads of the CTA after the barrier that follows staging and
 // after thread 0 has zeroed scratch.numLong / numWarpSeg before that barrier.
+template <int kIn>
 __device__ __forceinline__ void ReduceTile(const StagedTile& st, float* __restrict__ y, const SpmvPlanView& plan,
                                            const AclspSpmvParams& p, ReduceScratch& scratch)
 {
@@ -291,14 +306,16 @@ __device__ __forceinline__ void ReduceTile(const StagedTile& st, float* __restri
     };
     auto emit = [&](int k, double sum) {
         if (!Finite(sum)) {
-            sum = ExactSum(st.colInd, st.values, st.x, static_cast<int64_t>(st.j0) + segBegin(k),
-                           static_cast<int64_t>(st.j0) + segEnd(k), p.colIndStride, p.valuesStride, p.xStride,
-                           p.indexBase, p.cols);
+            sum = ExactSum<kIn>(st.colInd, st.values, st.x, static_cast<int64_t>(st.j0) + segBegin(k),
+                                static_cast<int64_t>(st.j0) + segEnd(k), p.colIndStride, p.valuesStride, p.xStride,
+                                p.indexBase, p.cols);
         }
         if (k >= nr) {
             plan.carry[2 * t] = sum;
         } else if (k == 0 && headOpen) {
             plan.carry[2 * t + 1] = sum;
+        } else if (kIn != kF32) {
+            StoreRowTyped(y, i0 + k, sum, sc, p);  // y addresses elements of p.yType; no mirrors
         } else {
             float* at = y + static_cast<int64_t>(i0 + k) * p.yStride;
             const float out = StoreRow(at, i0 + k, sum, sc, p);
@@ -474,19 +491,23 @@ __device__ __forceinline__ void ReduceTile(const StagedTile& st, float* __restri
 
 /* --------------------------------------------- one CTA per tile -- */
 
-template <bool kVector>
+// kIn != kF32: values, x and y address elements of the narrow types (see "element types" above); the
+// vector path then takes eight 2-byte values per 128-bit load.
+template <bool kVector, int kIn = kF32>
 __global__ void __launch_bounds__(kThreads, kVector ? 6 : 1)
 SpmvTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ values, const float* __restrict__ x,
                float* __restrict__ y, SpmvPlanView plan, AclspSpmvParams p, const uint32_t* __restrict__ maxRowLen,
                uint32_t rowBlockCap)
 {
+    static_assert(!kVector || kIn == kF32 || kIn == kF16 || kIn == kBF16, "vector loads: 4- and 2-byte values");
     if (rowBlockCap != 0 && *maxRowLen <= rowBlockCap) {
         return;  // every row is short: the row-block kernel computes this product
     }
     // One pool of 32-bit words: the hi parts of the tile's products, their lo
     // parts, and the tile's row offsets packed against the end.  A tile has nt
     // products and nr + 1 offsets with nt + nr <= kTile.
-    __shared__ __align__(16) float sPool[2 * kTile + 24];
+    constexpr int kVecElems = kIn == kF32 ? 4 : 8;  // elements of `values` per 128-bit load
+    __shared__ __align__(16) float sPool[2 * kTile + 40];
     __shared__ ReduceScratch scratch;
 
     const int tid = threadIdx.x;
@@ -514,13 +535,13 @@ SpmvTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ val
     }
     // Products are stored at their offset from the 4-aligned array index a0,
     // so that a 128-bit load of the arrays maps onto a 128-bit shared store.
-    const int a0 = kVector ? (j0 & ~3) : j0;
+    const int a0 = kVector ? (j0 & ~(kVecElems - 1)) : j0;
     const int shift = j0 - a0;
-    const int span = (nt + shift + 3) & ~3;
+    const int span = (nt + shift + kVecElems - 1) & ~(kVecElems - 1);
     float* sHi = sPool;
     float* sLo = sPool + span;
-    int* sOff = reinterpret_cast<int*>(sPool + 2 * kTile + 24) - (nr + 2);
-    // nr more words fit between the products and the offsets (2 * span <= 2 * nt + 12 and
+    int* sOff = reinterpret_cast<int*>(sPool + 2 * kTile + 40) - (nr + 2);
+    // nr more words fit between the products and the offsets (2 * span <= 2 * nt + 28 and
     // nt + nr <= kTile): the finished rows' values, kept for the mirrors of y.
     float* sOut = reinterpret_cast<float*>(sOff) - nr;
     if (tid == 0) {
@@ -532,7 +553,53 @@ SpmvTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ val
         sOff[k] = ClampOffset(plan.rowPtr[i0 + k], nnz) - j0;
     }
 
-    if (kVector) {
+    if constexpr (kVector && kIn != kF32) {
+        // Eight 2-byte values and eight column indices per step: one 128-bit load of the values, two
+        // of the indices; elements of the first and last vector that belong to a neighbouring tile
+        // are multiplied too, nothing reads their slots.
+        const int nvec = span >> 3;
+        for (int v = tid; v < nvec; v += kThreads) {
+            const int e = a0 + 8 * v;
+            int32_t c[8];
+            float w[8];
+            if (e + 8 <= nnz) {
+                const int4 c0 = __ldcs(reinterpret_cast<const int4*>(colInd + e));
+                const int4 c1 = __ldcs(reinterpret_cast<const int4*>(colInd + e + 4));
+                const uint4 raw = __ldcs(reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(values) + e));
+                c[0] = c0.x; c[1] = c0.y; c[2] = c0.z; c[3] = c0.w;
+                c[4] = c1.x; c[5] = c1.y; c[6] = c1.z; c[7] = c1.w;
+                const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    if constexpr (kIn == kF16) {
+                        const __half2 h = *reinterpret_cast<const __half2*>(&words[q]);
+                        w[2 * q] = __low2float(h);
+                        w[2 * q + 1] = __high2float(h);
+                    } else {  // bf16: the upper half of an fp32
+                        w[2 * q] = __uint_as_float(words[q] << 16);
+                        w[2 * q + 1] = __uint_as_float(words[q] & 0xffff0000u);
+                    }
+                }
+            } else {  // the last vector of the arrays may be partial
+#pragma unroll
+                for (int q = 0; q < 8; ++q) {
+                    const bool in = e + q < nnz;
+                    c[q] = in ? __ldcs(colInd + e + q) : -1;
+                    w[q] = in ? LoadIn<kIn>(values, e + q) : 0.0f;
+                }
+            }
+            float hi[8];
+            float lo[8];
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+                Product<kIn>(w[q], c[q], x, p.indexBase, p.cols, 1, hi[q], lo[q]);
+            }
+            *reinterpret_cast<float4*>(sHi + 8 * v) = make_float4(hi[0], hi[1], hi[2], hi[3]);
+            *reinterpret_cast<float4*>(sHi + 8 * v + 4) = make_float4(hi[4], hi[5], hi[6], hi[7]);
+            *reinterpret_cast<float4*>(sLo + 8 * v) = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            *reinterpret_cast<float4*>(sLo + 8 * v + 4) = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        }
+    } else if constexpr (kVector) {
         const int nvec = span >> 2;
         struct Vec4 {
             int4 c;
@@ -591,8 +658,8 @@ SpmvTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ val
     } else {
         for (int k = tid; k < nt; k += kThreads) {
             const int64_t e = static_cast<int64_t>(j0) + k;
-            Product(values[e * p.valuesStride], colInd[e * p.colIndStride], x, p.indexBase, p.cols, p.xStride,
-                    sHi[k], sLo[k]);
+            Product<kIn>(LoadIn<kIn>(values, e * p.valuesStride), colInd[e * p.colIndStride], x, p.indexBase, p.cols,
+                         p.xStride, sHi[k], sLo[k]);
         }
     }
     __syncthreads();
@@ -612,7 +679,7 @@ SpmvTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ val
     st.loT = sLo + shift;
     st.sOff = sOff;
     st.sOut = sOut;
-    ReduceTile(st, y, plan, p, scratch);
+    ReduceTile<kIn>(st, y, plan, p, scratch);
 }
 
 /* ------------------------------------------------ row blocks (A) -- */
@@ -621,11 +688,16 @@ constexpr int kBlockRows = 32;             // rows per block: one per lane
 constexpr int kOffsetWords = 36;           // 33 row offsets, rounded up to whole 16-byte vectors
 constexpr uint32_t kSpinLimit = 1u << 18;  // polls of about a microsecond before a wait is given up
 
-// Words of one stage for rows of at most `cap` non-zeros: the offsets, then the slice of
-// values and the slice of colInd, each from the 4-aligned array index below the block's first
-// non-zero to the 4-aligned index above its last.
-__host__ __device__ constexpr int RowBlockSpanCap(int cap) { return kBlockRows * cap + 8; }
-__host__ __device__ constexpr int RowBlockStageWords(int cap) { return kOffsetWords + 2 * RowBlockSpanCap(cap); }
+// Elements of one stage slice for rows of at most `cap` non-zeros, and the words of a stage: the
+// offsets, then the slice of values and the slice of colInd, each from the aligned array index below
+// the block's first non-zero to the aligned index above its last.  `align` is the number of elements
+// of `values` in 16 bytes (4 for fp32, 8 for the 2-byte types): slices start and end on multiples of it,
+// so that both bulk copies start on a 16-byte boundary and have a multiple of 16 bytes.
+__host__ __device__ constexpr int RowBlockSpanCap(int cap, int align) { return kBlockRows * cap + 2 * align; }
+__host__ __device__ constexpr int RowBlockStageWords(int cap, int align)
+{
+    return kOffsetWords + RowBlockSpanCap(cap, align) + RowBlockSpanCap(cap, align) * 4 / align;
+}
 constexpr int kRowBlockMaxLen = 40;  // longest row the row-block kernel is used for
 
 __device__ __forceinline__ uint32_t SharedAddress(const void* ptr)
@@ -678,7 +750,7 @@ __device__ __forceinline__ bool WaitStage(uint64_t* bar, uint32_t parity)
 struct RowBlockGeom {
     int r0;         // first row
     int nrows;      // rows in the block (32 except at the end of the matrix)
-    int a0;         // 4-aligned array index the staged slices start at
+    int a0;         // aligned array index the staged slices start at
     int span;       // words staged per slice
     int copyElems;  // leading part of the span that is whole vectors inside the arrays: bulk-copied
     int offWords;   // row offsets copied, whole vectors
@@ -687,7 +759,7 @@ struct RowBlockGeom {
 
 // j0 / j1: offsets of the block's first row and of the row after its last one, as loaded from the plan.
 __device__ __forceinline__ RowBlockGeom BlockGeometry(uint32_t block, int j0, int j1, const AclspSpmvParams& p,
-                                                      int spanCap)
+                                                      int spanCap, int align)
 {
     RowBlockGeom g;
     const int nnz = static_cast<int>(p.nnz);
@@ -696,29 +768,32 @@ __device__ __forceinline__ RowBlockGeom BlockGeometry(uint32_t block, int j0, in
     g.nrows = left < kBlockRows ? left : kBlockRows;
     j0 = ClampOffset(j0, nnz);
     j1 = ClampOffset(j1, nnz);
-    g.a0 = j0 & ~3;
-    g.span = (j1 - g.a0 + 3) & ~3;
+    g.a0 = j0 & ~(align - 1);
+    g.span = (j1 - g.a0 + align - 1) & ~(align - 1);
     g.valid = j1 >= j0 && g.span <= spanCap;
-    const int whole = (nnz & ~3) - g.a0;
+    const int whole = (nnz & ~(align - 1)) - g.a0;
     g.copyElems = whole < 0 ? 0 : (whole < g.span ? whole : g.span);
     g.offWords = (g.nrows + 1 + 3) & ~3;
     return g;
 }
 
 // Lane 0: announce the bytes of a block to the stage's barrier and start its copies.
+// valueBytes: size of an element of `values` (4 or 2).
 __device__ __forceinline__ void IssueBlock(const RowBlockGeom& g, float* stage, int spanCap, uint64_t* bar,
-                                           const int32_t* colInd, const float* values, const int32_t* rowPtr,
-                                           uint64_t policy)
+                                           const int32_t* colInd, const void* values, const int32_t* rowPtr,
+                                           uint64_t policy, uint32_t valueBytes)
 {
-    const uint32_t arrayBytes = g.valid ? 4u * static_cast<uint32_t>(g.copyElems) : 0u;
+    const uint32_t colBytes = g.valid ? 4u * static_cast<uint32_t>(g.copyElems) : 0u;
+    const uint32_t valBytes = g.valid ? valueBytes * static_cast<uint32_t>(g.copyElems) : 0u;
     const uint32_t offBytes = 4u * static_cast<uint32_t>(g.offWords);
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(SharedAddress(bar)),
-                 "r"(2u * arrayBytes + offBytes)
+                 "r"(colBytes + valBytes + offBytes)
                  : "memory");
     BulkLoad(stage, rowPtr + g.r0, offBytes, bar, policy);
-    if (arrayBytes != 0) {
-        BulkLoad(stage + kOffsetWords, values + g.a0, arrayBytes, bar, policy);
-        BulkLoad(stage + kOffsetWords + spanCap, colInd + g.a0, arrayBytes, bar, policy);
+    if (colBytes != 0) {
+        BulkLoad(stage + kOffsetWords, static_cast<const unsigned char*>(values) + static_cast<size_t>(g.a0) * valueBytes,
+                 valBytes, bar, policy);
+        BulkLoad(stage + kOffsetWords + spanCap * valueBytes / 4u, colInd + g.a0, colBytes, bar, policy);
     }
 }
 
@@ -726,17 +801,22 @@ __device__ __forceinline__ void IssueBlock(const RowBlockGeom& g, float* stage, 
 // per CTA, each with its own kStages stages; the launcher sizes the grid so that the stages of the
 // resident CTAs fill shared memory.  checkPlan != 0: return at once unless the plan header says that
 // no row is longer than cap (the host did not know yet which kernel the matrix needs).
-template <int kStages, int kWarpsPerCta, int kUnroll>
+// kIn: fp32, or one of the 2-byte types (values, x and y then address elements of those types).
+template <int kStages, int kWarpsPerCta, int kUnroll, int kIn = kF32>
 __global__ void __launch_bounds__(32 * kWarpsPerCta)
 SpmvRowBlockKernel(const int32_t* __restrict__ colInd, const float* __restrict__ values, const float* __restrict__ x,
                    float* __restrict__ y, SpmvPlanView plan, AclspSpmvParams p, const uint32_t* __restrict__ maxRowLen,
                    uint32_t* __restrict__ waitFailures, int cap, int checkPlan)
 {
+    static_assert(kIn == kF32 || kIn == kF16 || kIn == kBF16, "bulk-copied slices: 4- and 2-byte values");
+    constexpr int kAlign = kIn == kF32 ? 4 : 8;         // elements of `values` in 16 bytes
+    constexpr uint32_t kValueBytes = kIn == kF32 ? 4u : 2u;
+    using StagedValue = typename std::conditional<kIn == kF32, float, uint16_t>::type;
     if (checkPlan != 0 && *maxRowLen > static_cast<uint32_t>(cap)) {
         return;  // some row is too long for a stage: the merge-path tiles compute this product
     }
-    const int kSpanCap = RowBlockSpanCap(cap);
-    const int kWords = RowBlockStageWords(cap);
+    const int kSpanCap = RowBlockSpanCap(cap, kAlign);
+    const int kWords = RowBlockStageWords(cap, kAlign);
     extern __shared__ __align__(128) unsigned char smemRaw[];
     const int lane = threadIdx.x & 31;
     const int warpInCta = threadIdx.x >> 5;
@@ -765,8 +845,8 @@ SpmvRowBlockKernel(const int32_t* __restrict__ colInd, const float* __restrict__
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
         uint32_t b = firstBlock;
         for (int s = 0; s < kStages && b < numBlocks; ++s, b += totalWarps) {
-            const RowBlockGeom g = BlockGeometry(b, rowPtr[b * kBlockRows], rowPtr[lastRowOf(b)], p, kSpanCap);
-            IssueBlock(g, ring + s * kWords, kSpanCap, full + s, colInd, values, rowPtr, policy);
+            const RowBlockGeom g = BlockGeometry(b, rowPtr[b * kBlockRows], rowPtr[lastRowOf(b)], p, kSpanCap, kAlign);
+            IssueBlock(g, ring + s * kWords, kSpanCap, full + s, colInd, values, rowPtr, policy, kValueBytes);
         }
     }
     __syncwarp();
@@ -777,9 +857,13 @@ SpmvRowBlockKernel(const int32_t* __restrict__ colInd, const float* __restrict__
     auto slowRow = [&](int row) {
         const int b = ClampOffset(rowPtr[row], nnz);
         const int e = ClampOffset(rowPtr[row + 1], nnz);
-        return ExactSum(colInd, values, x, b, e, 1, 1, 1, p.indexBase, p.cols);
+        return ExactSum<kIn>(colInd, values, x, b, e, 1, 1, 1, p.indexBase, p.cols);
     };
     auto writeRow = [&](int row, double sum) {
+        if (kIn != kF32) {
+            StoreRowTyped(y, row, sum, sc, p);  // y addresses elements of p.yType; no mirrors
+            return;
+        }
         float* at = y + static_cast<int64_t>(row) * p.yStride;
         const float out = StoreRow(at, row, sum, sc, p);
         if (p.numMirrors != 0) {
@@ -818,23 +902,33 @@ SpmvRowBlockKernel(const int32_t* __restrict__ colInd, const float* __restrict__
             continue;
         }
         const int* off = reinterpret_cast<const int*>(stage);
-        const RowBlockGeom g = BlockGeometry(block, off[0], off[lastRowOf(block) - r0], p, kSpanCap);
+        const RowBlockGeom g = BlockGeometry(block, off[0], off[lastRowOf(block) - r0], p, kSpanCap, kAlign);
         if (!g.valid) {
             if (rowOk) {
                 writeRow(row, slowRow(row));
             }
         } else {
-            float* sVal = stage + kOffsetWords;
-            int* sCol = reinterpret_cast<int*>(stage + kOffsetWords + kSpanCap);
+            StagedValue* sVal = reinterpret_cast<StagedValue*>(stage + kOffsetWords);
+            int* sCol = reinterpret_cast<int*>(stage + kOffsetWords + kSpanCap * static_cast<int>(kValueBytes) / 4);
             if (g.copyElems < g.span) {
                 // The arrays end inside this span with a partial vector: plain loads fill it.
                 for (int k = g.copyElems + lane; k < g.span; k += 32) {
                     const int e = g.a0 + k;
                     sCol[k] = e < nnz ? __ldcs(colInd + e) : -1;
-                    sVal[k] = e < nnz ? __ldcs(values + e) : 0.0f;
+                    sVal[k] = e < nnz ? __ldcs(reinterpret_cast<const StagedValue*>(values) + e) : StagedValue(0);
                 }
                 __syncwarp();
             }
+            // A staged value as fp32 (exact).
+            auto widen = [](StagedValue v) {
+                if constexpr (kIn == kF16) {
+                    return __half2float(__ushort_as_half(v));
+                } else if constexpr (kIn == kBF16) {
+                    return __uint_as_float(static_cast<uint32_t>(v) << 16);
+                } else {
+                    return v;
+                }
+            };
             int b = 0, e = 0;
             if (rowOk) {
                 b = ClampOffset(off[lane], nnz) - g.a0;
@@ -854,19 +948,21 @@ SpmvRowBlockKernel(const int32_t* __restrict__ colInd, const float* __restrict__
                 for (int u = 0; u < kUnroll; ++u) {
                     const bool ok = q + u < e;
                     cc[u] = ok ? sCol[q + u] : -1;
-                    vv[u] = ok ? sVal[q + u] : 0.0f;
+                    vv[u] = ok ? widen(sVal[q + u]) : 0.0f;
                 }
 #pragma unroll
                 for (int u = 0; u < kUnroll; ++u) {
                     const uint32_t col = static_cast<uint32_t>(cc[u]) - p.indexBase;
                     const bool in = col < p.cols;
-                    xx[u] = in ? __ldg(x + col) : 0.0f;
+                    xx[u] = in ? LoadIn<kIn>(x, col) : 0.0f;
                     vv[u] = in ? vv[u] : 0.0f;
                 }
 #pragma unroll
                 for (int u = 0; u < kUnroll; ++u) {
                     const float hi = __fmul_rn(vv[u], xx[u]);
-                    l += fmaf(vv[u], xx[u], -hi);
+                    if (kIn == kF32) {  // products of the narrow types are exact
+                        l += fmaf(vv[u], xx[u], -hi);
+                    }
                     h += static_cast<double>(hi);
                 }
                 q += kUnroll;
@@ -874,8 +970,8 @@ SpmvRowBlockKernel(const int32_t* __restrict__ colInd, const float* __restrict__
             if (rowOk) {
                 double sum = h + static_cast<double>(l);
                 if (!Finite(sum)) {
-                    sum = ExactSum(colInd, values, x, static_cast<int64_t>(g.a0) + b, static_cast<int64_t>(g.a0) + e, 1,
-                                   1, 1, p.indexBase, p.cols);
+                    sum = ExactSum<kIn>(colInd, values, x, static_cast<int64_t>(g.a0) + b,
+                                        static_cast<int64_t>(g.a0) + e, 1, 1, 1, p.indexBase, p.cols);
                 }
                 writeRow(row, sum);
             }
@@ -884,8 +980,8 @@ SpmvRowBlockKernel(const int32_t* __restrict__ colInd, const float* __restrict__
         if (lane == 0 && refill < numBlocks) {
             // Shared-memory reads of the block above come before the copy engine's writes.
             asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-            const RowBlockGeom r = BlockGeometry(refill, refillJ0, refillJ1, p, kSpanCap);
-            IssueBlock(r, stage, kSpanCap, full + s, colInd, values, rowPtr, policy);
+            const RowBlockGeom r = BlockGeometry(refill, refillJ0, refillJ1, p, kSpanCap, kAlign);
+            IssueBlock(r, stage, kSpanCap, full + s, colInd, values, rowPtr, policy, kValueBytes);
         }
     }
     if (waitedOut) {
@@ -910,6 +1006,7 @@ SpmvRowBlockKernel(const int32_t* __restrict__ colInd, const float* __restrict__
 // crossed several tiles are then taken one by one by the whole warp: the lanes add the carry-outs
 // of the tiles the row crossed (lane-strided, then a shuffle tree: a fixed order), lane 0 adds the
 // head partial and writes the row.
+template <int kIn = kF32>
 __global__ void __launch_bounds__(kThreads)
 SpmvCarryFixupKernel(float* __restrict__ y, SpmvPlanView plan, AclspSpmvParams p, const uint32_t* __restrict__ maxRowLen,
                      uint32_t rowBlockCap)
@@ -924,6 +1021,10 @@ SpmvCarryFixupKernel(float* __restrict__ y, SpmvPlanView plan, AclspSpmvParams p
     const int64_t total = static_cast<int64_t>(p.rows) + nnz;
     const Scalars sc = LoadScalars(p);
     auto writeRow = [&](int row, double sum) {
+        if (kIn != kF32) {
+            StoreRowTyped(y, row, sum, sc, p);
+            return;
+        }
         float* at = y + static_cast<int64_t>(row) * p.yStride;
         const float out = StoreRow(at, row, sum, sc, p);
         if (p.numMirrors != 0) {
@@ -985,10 +1086,12 @@ int EnvInt(const char* name, int fallback)
     return e == nullptr ? fallback : std::atoi(e);
 }
 
+template <int kIn>
 void LaunchRowBlocks(const void* colInd, const void* values, const void* x, void* y, const SpmvPlanView& plan,
                      const AclspSpmvParams& p, const uint32_t* maxRowLen, uint32_t* waitFailures, int cap, bool checkPlan,
                      cudaStream_t s)
 {
+    constexpr int kAlign = kIn == kF32 ? 4 : 8;
     constexpr int kStages = 1;
     constexpr int kWarpsPerCta = 2;
     constexpr int kUnroll = 16;
@@ -998,9 +1101,9 @@ void LaunchRowBlocks(const void* colInd, const void* values, const void* x, void
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms <= 0) {
         sms = 148;
     }
-    const size_t smem = sizeof(float) * kWarpsPerCta * kStages * RowBlockStageWords(cap) +
+    const size_t smem = sizeof(float) * kWarpsPerCta * kStages * RowBlockStageWords(cap, kAlign) +
                         sizeof(uint64_t) * kWarpsPerCta * kStages;
-    auto kernel = SpmvRowBlockKernel<kStages, kWarpsPerCta, kUnroll>;
+    auto kernel = SpmvRowBlockKernel<kStages, kWarpsPerCta, kUnroll, kIn>;
     cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     // Resident CTAs per SM: what shared memory holds (a CTA also takes 1 KiB of system shared memory),
     // at most 32 CTAs and 32 warps of this register footprint.
@@ -1016,30 +1119,14 @@ void LaunchRowBlocks(const void* colInd, const void* values, const void* x, void
         static_cast<float*>(y), plan, p, maxRowLen, waitFailures, cap, checkPlan ? 1 : 0);
 }
 
-}  // namespace
-
-extern "C" void spmv_b200_kernel_do(const void* colInd, const void* values, const void* x, void* y,
-                                    void* workspace, const AclspSpmvParams* params, void* stream)
+// One product of element type kIn: picks the kernel (see spmv_b200_kernel_do) and launches it.
+template <int kIn>
+void LaunchProduct(const void* colInd, const void* values, const void* x, void* y, void* workspace,
+                   const SpmvPlanView& plan, const AclspSpmvParams& p, cudaStream_t s)
 {
-    auto s = static_cast<cudaStream_t>(stream);
-    AclspSpmvParams p = *params;
-    // Bit 1 of mirrorMulticast (internal): send a tile's finished rows to the mirrors as one contiguous
-    // run of 16-byte vectors after the tile, instead of row by row as they are produced.  Row by row costs
-    // the kernel nothing but arrives as 32- to 64-byte packets (about 185 GB/s into a B200, measured), enough
-    // for one or two peers; batching costs a barrier per tile (+10 % kernel time) and is what keeps 8 GPUs
-    // fed.  ACLSPARSE_SPMV_MIRROR_BATCH=0 / 1 overrides the choice.
-    static const int batchEnv = [] {
-        const char* e = std::getenv("ACLSPARSE_SPMV_MIRROR_BATCH");
-        return e == nullptr ? -1 : (e[0] == '1' ? 1 : 0);
-    }();
-    const bool multicast = (p.mirrorMulticast & 1u) != 0;
-    const bool batch = batchEnv >= 0 ? batchEnv == 1 : (multicast || p.numMirrors >= 3);
-    p.mirrorMulticast = (multicast ? 1u : 0u) | (batch ? 2u : 0u);
-    const SpmvPlanView plan = MakeView(workspace, p.rows, p.nnz);
-    if (plan.numTiles == 0) {
-        return;
-    }
-    const bool vector = p.colIndStride == 1 && p.valuesStride == 1 && p.xStride == 1 &&
+    // 128-bit loads and bulk copies: 4- or 2-byte values, unit strides, 16-byte aligned arrays.
+    constexpr bool kCanVector = kIn == kF32 || kIn == kF16 || kIn == kBF16;
+    const bool vector = kCanVector && p.colIndStride == 1 && p.valuesStride == 1 && p.xStride == 1 &&
                         reinterpret_cast<uintptr_t>(colInd) % 16 == 0 && reinterpret_cast<uintptr_t>(values) % 16 == 0;
     auto* header = static_cast<unsigned char*>(workspace);
     const auto* maxRowLen = reinterpret_cast<const uint32_t*>(header + ACLSP_HEADER_MAX_ROW_LEN_OFF);
@@ -1065,26 +1152,68 @@ extern "C" void spmv_b200_kernel_do(const void* colInd, const void* values, cons
         cap = mean8 <= 8u * 14u ? 16u : (mean8 <= 8u * 28u ? 32u : 0u);
         checkPlan = cap != 0;
     }
-    if (cap != 0) {
-        LaunchRowBlocks(colInd, values, x, y, plan, p, maxRowLen, waitFailures, static_cast<int>(cap), checkPlan, s);
-        if (!checkPlan) {
-            return;
+    if constexpr (kCanVector) {
+        if (cap != 0) {
+            LaunchRowBlocks<kIn>(colInd, values, x, y, plan, p, maxRowLen, waitFailures, static_cast<int>(cap), checkPlan,
+                                 s);
+            if (!checkPlan) {
+                return;
+            }
         }
     }
     const uint32_t tileCap = checkPlan ? cap : 0u;
-    if (vector) {
-        AclspCountLaunches(1);
-        SpmvTileKernel<true><<<plan.numTiles, kThreads, 0, s>>>(
-            static_cast<const int32_t*>(colInd), static_cast<const float*>(values), static_cast<const float*>(x),
-            static_cast<float*>(y), plan, p, maxRowLen, tileCap);
-    } else {
-        AclspCountLaunches(1);
-        SpmvTileKernel<false><<<plan.numTiles, kThreads, 0, s>>>(
-            static_cast<const int32_t*>(colInd), static_cast<const float*>(values), static_cast<const float*>(x),
-            static_cast<float*>(y), plan, p, maxRowLen, tileCap);
+    const auto* ci = static_cast<const int32_t*>(colInd);
+    const auto* va = static_cast<const float*>(values);  // typed by kIn inside the kernels
+    const auto* xv = static_cast<const float*>(x);
+    auto* yv = static_cast<float*>(y);
+    AclspCountLaunches(2);
+    bool launched = false;
+    if constexpr (kCanVector) {
+        if (vector) {
+            SpmvTileKernel<true, kIn><<<plan.numTiles, kThreads, 0, s>>>(ci, va, xv, yv, plan, p, maxRowLen, tileCap);
+            launched = true;
+        }
+    }
+    if (!launched) {
+        SpmvTileKernel<false, kIn><<<plan.numTiles, kThreads, 0, s>>>(ci, va, xv, yv, plan, p, maxRowLen, tileCap);
     }
     const uint32_t fixupWarps = (plan.numTiles + 31u) / 32u;
-    AclspCountLaunches(1);
-    SpmvCarryFixupKernel<<<(fixupWarps + kWarps - 1u) / kWarps, kThreads, 0, s>>>(static_cast<float*>(y), plan, p,
-                                                                                 maxRowLen, tileCap);
+    SpmvCarryFixupKernel<kIn><<<(fixupWarps + kWarps - 1u) / kWarps, kThreads, 0, s>>>(yv, plan, p, maxRowLen, tileCap);
+}
+
+}  // namespace
+
+extern "C" void spmv_b200_kernel_do(const void* colInd, const void* values, const void* x, void* y,
+                                    void* workspace, const AclspSpmvParams* params, void* stream)
+{
+    auto s = static_cast<cudaStream_t>(stream);
+    AclspSpmvParams p = *params;
+    // Bit 1 of mirrorMulticast (internal): send a tile's finished rows to the mirrors as one contiguous
+    // run of 16-byte vectors after the tile, instead of row by row as they are produced.  Row by row costs
+    // the kernel nothing but arrives as 32- to 64-byte packets (about 185 GB/s into a B200, measured), enough
+    // for one or two peers; batching costs a barrier per tile (+10 % kernel time) and is what keeps 8 GPUs
+    // fed.  ACLSPARSE_SPMV_MIRROR_BATCH=0 / 1 overrides the choice.
+    static const int batchEnv = [] {
+        const char* e = std::getenv("ACLSPARSE_SPMV_MIRROR_BATCH");
+        return e == nullptr ? -1 : (e[0] == '1' ? 1 : 0);
+    }();
+    const bool multicast = (p.mirrorMulticast & 1u) != 0;
+    const bool batch = batchEnv >= 0 ? batchEnv == 1 : (multicast || p.numMirrors >= 3);
+    p.mirrorMulticast = (multicast ? 1u : 0u) | (batch ? 2u : 0u);
+    const SpmvPlanView plan = MakeView(workspace, p.rows, p.nnz);
+    if (plan.numTiles == 0) {
+        return;
+    }
+    if (p.valueType == ACLSP_TYPE_F32) {
+        LaunchProduct<kF32>(colInd, values, x, y, workspace, plan, p, s);
+        return;
+    }
+    p.numMirrors = 0;  // mirrors of y are for fp32 products
+    if (p.valueType == ACLSP_TYPE_F16) {
+        LaunchProduct<kF16>(colInd, values, x, y, workspace, plan, p, s);
+    } else if (p.valueType == ACLSP_TYPE_BF16) {
+        LaunchProduct<kBF16>(colInd, values, x, y, workspace, plan, p, s);
+    } else if (p.valueType == ACLSP_TYPE_I8) {
+        LaunchProduct<kI8>(colInd, values, x, y, workspace, plan, p, s);
+    }
 }

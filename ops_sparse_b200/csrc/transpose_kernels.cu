@@ -270,15 +270,26 @@ __global__ void FillTransposedColumnsKernel(const int32_t* __restrict__ perm, co
 
 // valuesT[p] = values[perm[p]]; slots beyond the kept entries are zeroed so that nothing
 // uninitialised is ever multiplied.
-__global__ void GatherValuesKernel(const float* __restrict__ values, int64_t valuesStride,
+// T: an unsigned integer as wide as an element (the bits are moved, not interpreted; zero bits are 0 in
+// every element type).
+template <typename T>
+__global__ void GatherValuesKernel(const T* __restrict__ values, int64_t valuesStride,
                                    const int32_t* __restrict__ perm, const int32_t* __restrict__ rowPtrT, uint32_t cols,
-                                   uint32_t nnz, float* __restrict__ valuesT)
+                                   uint32_t nnz, T* __restrict__ valuesT)
 {
     const uint64_t kept = static_cast<uint64_t>(rowPtrT[cols]);
     const uint64_t step = static_cast<uint64_t>(gridDim.x) * blockDim.x;
     for (uint64_t p = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; p < nnz; p += step) {
-        valuesT[p] = p < kept ? values[static_cast<int64_t>(perm[p]) * valuesStride] : 0.0f;
+        valuesT[p] = p < kept ? values[static_cast<int64_t>(perm[p]) * valuesStride] : static_cast<T>(0);
     }
+}
+
+template <typename T>
+void LaunchGatherValues(const void* values, int64_t valuesStride, const int32_t* perm, const int32_t* rowPtrT,
+                        uint32_t cols, uint32_t nnz, void* valuesT, unsigned grid, cudaStream_t s)
+{
+    GatherValuesKernel<T><<<grid, 256, 0, s>>>(static_cast<const T*>(values), valuesStride, perm, rowPtrT, cols, nnz,
+                                              static_cast<T*>(valuesT));
 }
 
 unsigned GridFor(uint64_t items, unsigned perBlock)
@@ -345,15 +356,24 @@ extern "C" void aclsp_b200_transpose_build_kernel_do(const void* rowPtr, const v
 
 extern "C" void aclsp_b200_transpose_values_kernel_do(const void* values, int64_t valuesStride, uint32_t cols,
                                                       uint32_t nnz, void* workspace,
-                                                      const AclspTransposeLayout* layout, void* stream)
+                                                      const AclspTransposeLayout* layout, uint32_t elemBytes,
+                                                      void* stream)
 {
     if (nnz == 0) {
         return;
     }
     auto* base = static_cast<unsigned char*>(workspace);
+    const auto* perm = reinterpret_cast<const int32_t*>(base + layout->permOff);
+    const auto* rowPtrT = reinterpret_cast<const int32_t*>(base + layout->rowPtrOff);
+    void* valuesT = base + layout->valuesOff;
+    const unsigned grid = GridFor(nnz, 256);
+    auto s = static_cast<cudaStream_t>(stream);
     AclspCountLaunches(1);
-    GatherValuesKernel<<<GridFor(nnz, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const float*>(values), valuesStride, reinterpret_cast<const int32_t*>(base + layout->permOff),
-        reinterpret_cast<const int32_t*>(base + layout->rowPtrOff), cols, nnz,
-        reinterpret_cast<float*>(base + layout->valuesOff));
+    if (elemBytes == 1) {
+        LaunchGatherValues<uint8_t>(values, valuesStride, perm, rowPtrT, cols, nnz, valuesT, grid, s);
+    } else if (elemBytes == 2) {
+        LaunchGatherValues<uint16_t>(values, valuesStride, perm, rowPtrT, cols, nnz, valuesT, grid, s);
+    } else {
+        LaunchGatherValues<uint32_t>(values, valuesStride, perm, rowPtrT, cols, nnz, valuesT, grid, s);
+    }
 }

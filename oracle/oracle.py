@@ -282,6 +282,68 @@ def row_block_bounds(row_ptr, nnz: int, parts: int, index_base=0) -> np.ndarray:
     return bounds
 
 
+# ---------------------------------------------------------- narrow types --
+# fp16 / bf16 / int8 storage (the reference's table, sparse/spmv/arch35/spmv_host.cpp:44-66).  Every such
+# value is exactly an fp32 number, so the fp64 truth of a narrow product is spmv_f64 on the widened arrays;
+# what differs is the rounding of the result, restated here: to nearest, ties to even, once
+# (sparse/spmv/arch35/spmv_kernel.cpp:104-160 for the two 16-bit formats), and the saturating integer form.
+
+def bf16_bits_to_f32(bits) -> np.ndarray:
+    """bf16 bit patterns (uint16) as fp32 numbers: a bf16 is the upper half of an fp32."""
+    return (np.asarray(bits, dtype=np.uint16).astype(np.uint32) << 16).view(np.float32)
+
+
+def f32_to_bf16_bits(v) -> np.ndarray:
+    """fp32 -> bf16 bit patterns, to nearest even (NaN stays NaN)."""
+    b = np.ascontiguousarray(v, dtype=np.float32).view(np.uint32)
+    rounded = ((b.astype(np.uint64) + 0x7FFF + ((b >> 16) & 1)) >> 16).astype(np.uint16)
+    nan = np.isnan(np.asarray(v, dtype=np.float32))
+    return np.where(nan, np.uint16(0x7FC0), rounded)
+
+
+def f64_to_bf16_bits(v) -> np.ndarray:
+    """fp64 -> bf16 with ONE rounding to nearest even: the double is first rounded to fp32 to odd (truncate
+    toward zero, set the last bit when inexact), which keeps enough information for the final rounding."""
+    v = np.ascontiguousarray(v, dtype=np.float64)
+    with np.errstate(over="ignore", invalid="ignore"):
+        f = v.astype(np.float32)
+        too_big = np.isfinite(f) & (np.abs(f.astype(np.float64)) > np.abs(v))
+        f = np.where(too_big, np.nextafter(f, np.float32(0)), f).astype(np.float32)
+        inexact = np.isfinite(f) & (f.astype(np.float64) != v)
+    bits = f.view(np.uint32) | inexact.astype(np.uint32)
+    # a finite double beyond the fp32 range rounds to infinity in bf16 as well
+    with np.errstate(over="ignore"):
+        overflow = np.isfinite(v) & np.isinf(v.astype(np.float32))
+    out = f32_to_bf16_bits(bits.view(np.float32))
+    sign = (np.signbit(v).astype(np.uint16) << 15)
+    return np.where(overflow, sign | np.uint16(0x7F80), out)
+
+
+def f64_to_f16(v) -> np.ndarray:
+    """fp64 -> fp16, one rounding to nearest even (numpy converts from the double directly)."""
+    with np.errstate(over="ignore"):
+        return np.ascontiguousarray(v, dtype=np.float64).astype(np.float16)
+
+
+def spmv_i8_i32(row_ptr, col_ind, values, x, y, alpha: int, beta: int, index_base=0) -> np.ndarray:
+    """int8 data, int32 scalars and result: the exact integer alpha*sum + beta*y saturated to the int32 range
+    (the reference forms the same value by case analysis, sparse/spmv/arch35/spmv_kernel.cpp:347-375).
+    beta == 0 does not read y.  Python integers: exact at any size."""
+    row_ptr, col_ind = _i32(row_ptr), _i32(col_ind)
+    va = np.asarray(values, dtype=np.int64)
+    xv = np.asarray(x, dtype=np.int64)
+    rows = row_ptr.size - 1
+    out = np.empty(rows, dtype=np.int32)
+    for r in range(rows):
+        b, e = int(row_ptr[r]) - index_base, int(row_ptr[r + 1]) - index_base
+        cols = col_ind[b:e].astype(np.int64) - index_base
+        ok = (cols >= 0) & (cols < xv.size)
+        total = int(np.sum(va[b:e][ok] * xv[cols[ok]]))
+        val = int(alpha) * total + (int(beta) * int(y[r]) if beta != 0 else 0)
+        out[r] = max(-2**31, min(2**31 - 1, val))
+    return out
+
+
 # -------------------------------------------------------------- verifier --
 
 def check_tolerance(got, truth, rtol=RTOL, atol=ATOL):

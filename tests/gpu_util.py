@@ -2,6 +2,7 @@
 import numpy as np
 import torch
 
+from oracle import oracle as O
 from ops_sparse_b200 import _lib as L
 from ops_sparse_b200 import api
 
@@ -71,3 +72,41 @@ def random_csr(rng, lengths, cols):
     rp = np.concatenate([[0], np.cumsum(lengths)]).astype(np.int32)
     ci = np.concatenate([np.sort(rng.choice(cols, int(l), replace=False)) for l in lengths] or [[]]).astype(np.int32)
     return rp, ci
+
+
+# ---- narrow storage types: "f32", "f16", "bf16", "i8", "i32" ----
+
+def to_device(a, kind):
+    """A numpy array of exactly representable numbers as a device tensor of the named element type."""
+    if kind == "bf16":
+        bits = O.f32_to_bf16_bits(np.asarray(a, np.float32)).view(np.int16)
+        return dev(bits).view(torch.bfloat16)
+    np_type = {"f32": np.float32, "f16": np.float16, "i8": np.int8, "i32": np.int32}[kind]
+    return dev(np.asarray(a).astype(np_type))
+
+
+def bits_of(t):
+    """Result tensor -> numpy: 16-bit types as their bit patterns, the others as they are."""
+    if t.dtype in (torch.float16, torch.bfloat16):
+        return t.view(torch.int16).cpu().numpy().view(np.uint16)
+    return t.cpu().numpy()
+
+
+def quantize(a, kind):
+    """Round test data to the storage type and return it as fp32 (every narrow value is an fp32 number)."""
+    a = np.asarray(a, np.float32)
+    if kind == "f16":
+        return a.astype(np.float16).astype(np.float32)
+    if kind == "bf16":
+        return O.bf16_bits_to_f32(O.f32_to_bf16_bits(a))
+    if kind == "i8":
+        return np.clip(np.rint(a), -127, 127).astype(np.float32)
+    return a
+
+
+def expected_bits(truth, kind):
+    if kind == "f16":
+        return O.f64_to_f16(truth).view(np.uint16)
+    if kind == "bf16":
+        return O.f64_to_bf16_bits(truth)
+    return truth.astype(np.float32)
