@@ -61,7 +61,7 @@ FALLBACK_HBM_GBS = 6650.0
 # are from one full-size launch each.
 TRAFFIC_RATIO = {
     "c2": 224.06 / 223.71,   # SpmvRowBlockKernel, 1 M-row stencil
-    "c3": 273.9 / 272.24,    # SpmvTileKernel, 1 M-row power-law case
+    "c3": 286.29 / 285.02,   # SpmvTileKernel, 1 M-row power-law case
     "c4": 7.972 / 1.2122,    # SpmmTileKernel, one full-size launch
 }
 
@@ -555,6 +555,60 @@ def measure_narrow(ctx: Context, args, cfg: dict, kind: str, steps: int, warmup:
                       "max_rel_err": max_rel, "rtol": 1e-5, "atol": 1e-6}}
 
 
+def measure_col_slabs(ctx: Context, args, cfg: dict, width: int, steps: int, warmup: int) -> dict:
+    """The SpMM of `cfg` computed as n / width library calls, one per slab of `width` columns of B and C (dense
+    descriptors over the slab with the full leading dimension, so nothing is copied), one GPU.  A is streamed once
+    per slab; the point is whether a slab of B stays in L2 between the non-zeros that gather from it."""
+    from ops_sparse_b200 import api
+    torch = ctx.torch
+    dev = ctx.device
+    n, k, m = cfg["n"], cfg["cols"], cfg["rows"]
+    alpha, beta = cfg["alpha"], cfg["beta"]
+    rp = torch.from_numpy(cfg["row_ptr"]).to(dev)
+    ci = torch.from_numpy(cfg["col_ind"]).to(dev)
+    va = torch.from_numpy(cfg["values"]).to(dev)
+    b = torch.from_numpy(cfg["b"]).to(dev).view(k, n)
+    c0 = torch.from_numpy(cfg["c"]).to(dev).view(m, n)
+    c = c0.clone()
+    handle = api.Handle()
+    mat = api.CsrMatrix(m, k, rp, ci, va)
+    ops = []
+    for j in range(0, n, width):
+        w = min(width, n - j)
+        ops.append(api.SpMM(handle, mat, api.DnMat(k, w, n, b[:, j:j + w]), api.DnMat(m, w, n, c[:, j:j + w])))
+        ops[-1].preprocess(alpha, beta)
+
+    def step():
+        for op in ops:
+            op(alpha, beta)
+
+    step()
+    torch.cuda.synchronize()
+    check = None if args.no_check else check_whole_result(ctx, cfg, c, alpha, beta)
+    for _ in range(warmup):
+        step()
+    torch.cuda.synchronize()
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+    ends = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+    for i in range(steps):
+        if beta != 0.0:
+            c.copy_(c0)
+        starts[i].record()
+        step()
+        ends[i].record()
+    torch.cuda.synchronize()
+    ms = float(np.mean([s.elapsed_time(e) for s, e in zip(starts, ends)]))
+    peak, peak_kind = measured_peak()
+    abytes = workloads.algorithmic_bytes(cfg)
+    return {"metric": metric_name(cfg), "value": workloads.flops(cfg) / (ms * 1e-3) / 1e9, "unit": "GFLOP/s",
+            "ms_per_step": ms, "steps": steps, "warmup": warmup, "col_slab_width": width, "calls_per_step": len(ops),
+            "config": {"workload": describe(cfg) + f", as {len(ops)} calls on column slabs of {width}"},
+            "roofline": {"bound": "hbm", "achieved": abytes / (ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
+                         "frac": abytes / (ms * 1e-3) / 1e9 / peak, "peak_kind": peak_kind,
+                         "algorithmic_bytes_per_launch": abytes},
+            "check": check}
+
+
 def run_ours(args):
     ctx = Context(args)
     rank, world = ctx.rank, ctx.world
@@ -562,6 +616,12 @@ def run_ours(args):
     if rank == 0:
         sampler.start()
     cfg = make_workload(ctx, args.workload, args.rows)
+    if args.col_slabs:
+        if world != 1 or cfg["kind"] != "spmm":
+            raise SystemExit("--col-slabs: one GPU, an SpMM workload")
+        print(json.dumps(measure_col_slabs(ctx, args, cfg, args.col_slabs, max(3, min(args.steps, 10)), 3)))
+        cleanup_shared(ctx)
+        return
     head = measure(ctx, args, cfg, args.steps, args.warmup, 1.5)
     clocks = sampler.stop() if rank == 0 else None
     narrow = None
@@ -634,6 +694,8 @@ def main():
                     "replaying the step as one CUDA graph")
     ap.add_argument("--no-check", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--col-slabs", type=int, default=0, help="experiment: compute the SpMM workload as one call per "
+                    "slab of this many columns of B and C, print that measurement alone")
     ap.add_argument("--no-narrow", action="store_true", help="skip the fp16-storage variant of the headline workload")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup

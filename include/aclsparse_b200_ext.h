@@ -79,6 +79,19 @@ aclsparseStatus_t aclsparseB200NodeBarrier(aclrtStream stream, void* localState,
                                            int rank, unsigned spinLimit);
 aclsparseStatus_t aclsparseB200NodeBarrierStatus(aclrtStream stream, void* localState, int* missingRank);
 
+/* The same barrier as the END of every product written into `vec` / `mat`, instead of a kernel of its own:
+ * the last kernel of aclsparseSpMV / aclsparseSpMM (fp32) runs it in the CTA that finishes last, after
+ * that CTA has seen all others fence their stores, so a sharded step is the product kernels alone.  The
+ * arguments are those of aclsparseB200NodeBarrier; world <= 1 or localState == NULL removes it.  A product
+ * that has nothing to launch (no rows) runs no barrier: such a rank calls aclsparseB200NodeBarrier.  The
+ * wait is bounded as above and reported through aclsparseB200NodeBarrierStatus. */
+aclsparseStatus_t aclsparseB200DnVecSetClosingBarrier(aclsparseDnVecDescr_t vec, void* localState,
+                                                      void* const* peerStates, int world, int rank,
+                                                      unsigned spinLimit);
+aclsparseStatus_t aclsparseB200DnMatSetClosingBarrier(aclsparseDnMatDescr_t mat, void* localState,
+                                                      void* const* peerStates, int world, int rank,
+                                                      unsigned spinLimit);
+
 #if defined(__GNUC__)
 #pragma GCC visibility pop
 #endif

@@ -35,6 +35,21 @@ extern "C" {
  * the kind. */
 #define ACLSP_MAX_MIRRORS 7
 
+/* Closing barrier of a sharded product: with world > 1 the last kernel of the product ends with one node
+ * barrier (see aclsp_b200_node_barrier_kernel_do below for the protocol and the state), run by the CTA that
+ * finishes last, so that a step is the product kernels alone.  local: this rank's AclspNodeBarrierState;
+ * peers[r]: rank r's state as this device addresses it (entry `rank` unused); spinLimit: polls per peer
+ * before the wait is given up and local->status is set.  Zero-filled: no barrier. */
+#define ACLSP_BARRIER_MAX_RANKS 16
+typedef struct AclspBarrierLink {
+    void* local;
+    void* peers[ACLSP_BARRIER_MAX_RANKS];
+    uint32_t world;
+    uint32_t rank;
+    uint32_t spinLimit;
+    uint32_t reserved;
+} AclspBarrierLink;
+
 /* Per-launch parameters of the SpMV kernels.  Counterpart of the reference's
  * SpmvArch35TilingData (sparse/spmv/arch35/spmv_tiling_data.h:38-68), passed
  * by value as a kernel argument instead of being published to the workspace. */
@@ -75,6 +90,7 @@ typedef struct AclspSpmvParams {
     uint32_t computeInt;
     int32_t alphaInt;
     int32_t betaInt;
+    AclspBarrierLink barrier; /* closing barrier of a sharded product (fp32 only); world == 0: none */
 } AclspSpmvParams;
 
 #define ACLSP_MAX_ROW_LEN_UNKNOWN 0xFFFFFFFFu
@@ -115,6 +131,7 @@ typedef struct AclspSpmmParams {
     uint32_t computeInt;
     int32_t alphaInt;
     int32_t betaInt;
+    AclspBarrierLink barrier; /* closing barrier of a sharded product (fp32 only); world == 0: none */
 } AclspSpmmParams;
 
 /* Builds the SpMV plan in `workspace`: header, base-0 row offsets, merge-path
@@ -184,11 +201,10 @@ uint64_t aclsp_b200_kernel_launches(void);
  * symmetric memory), zero-filled before the first barrier.  epoch: barriers this rank has entered.
  * status: 0, or 1 + the rank that did not arrive within the limit of some barrier since the host last
  * looked.  flag[r]: the epoch rank r has announced to this rank. */
-#define ACLSP_BARRIER_MAX_RANKS 16
 typedef struct AclspNodeBarrierState {
     uint32_t epoch;
     uint32_t status;
-    uint32_t reserved[2];
+    uint32_t reserved[2];    /* [0]: CTA tickets of a closing barrier, zero between kernels */
     uint32_t flag[ACLSP_BARRIER_MAX_RANKS];
 } AclspNodeBarrierState;
 

@@ -53,6 +53,12 @@ def build() -> str:
     return LIB_PATH
 
 
+class BarrierLink(ctypes.Structure):
+    """AclspBarrierLink of include/aclsparse_b200_kernels.h."""
+    _fields_ = [("local", c_void_p), ("peers", c_void_p * 16), ("world", c_uint32), ("rank", c_uint32),
+                ("spinLimit", c_uint32), ("reserved", c_uint32)]
+
+
 class SpmvParams(ctypes.Structure):
     """AclspSpmvParams of include/aclsparse_b200_kernels.h."""
     _fields_ = [("rows", c_uint32), ("cols", c_uint32), ("nnz", c_uint32), ("indexBase", c_uint32),
@@ -61,7 +67,7 @@ class SpmvParams(ctypes.Structure):
                 ("numMirrors", c_uint32), ("mirrorMulticast", c_uint32), ("mirrorDelta", c_int64 * 7),
                 ("maxRowLenHint", c_uint32), ("betaSource", c_void_p), ("betaSourceStride", c_int64),
                 ("valueType", c_uint32), ("yType", c_uint32), ("computeInt", c_uint32),
-                ("alphaInt", ctypes.c_int32), ("betaInt", ctypes.c_int32)]
+                ("alphaInt", ctypes.c_int32), ("betaInt", ctypes.c_int32), ("barrier", BarrierLink)]
 
 
 # SpmvParams.valueType / yType
@@ -79,7 +85,7 @@ class SpmmParams(ctypes.Structure):
                 ("alphaPtr", c_void_p), ("betaPtr", c_void_p),
                 ("numMirrors", c_uint32), ("mirrorMulticast", c_uint32), ("mirrorDelta", c_int64 * 7),
                 ("valueType", c_uint32), ("cType", c_uint32), ("computeInt", c_uint32),
-                ("alphaInt", ctypes.c_int32), ("betaInt", ctypes.c_int32)]
+                ("alphaInt", ctypes.c_int32), ("betaInt", ctypes.c_int32), ("barrier", BarrierLink)]
 
 
 _P = c_void_p
@@ -175,6 +181,8 @@ SIGNATURES = {
     "aclsparseB200DnMatSetMulticastMirror": [_P, _P],
     "aclsparseB200NodeBarrier": [_P, _P, POINTER(c_void_p), c_int, c_int, c_uint32],
     "aclsparseB200NodeBarrierStatus": [_P, _P, POINTER(c_int)],
+    "aclsparseB200DnVecSetClosingBarrier": [_P, _P, POINTER(c_void_p), c_int, c_int, c_uint32],
+    "aclsparseB200DnMatSetClosingBarrier": [_P, _P, POINTER(c_void_p), c_int, c_int, c_uint32],
     # include/aclsparse_b200_kernels.h
     "spmv_b200_preprocess_kernel_do": [_P, _P, c_uint32, c_uint32, c_uint32, c_int32, c_int64, _P],
     "spmv_b200_kernel_do": [_P, _P, _P, _P, _P, POINTER(SpmvParams), _P],

@@ -138,6 +138,12 @@ class DnVec:
         check("aclsparseB200DnVecSetMulticastMirror",
               L.lib().aclsparseB200DnVecSetMulticastMirror(self._d, c_void_p(int(pointer))))
 
+    def set_closing_barrier(self, local_state: int, peer_states, world: int, rank: int, spin_limit: int = 0) -> None:
+        """Ends every SpMV into this vector with the node barrier (aclsparseB200DnVecSetClosingBarrier);
+        ``world <= 1`` removes it.  ``peer_states``: a ctypes array of ``world`` device addresses."""
+        check("aclsparseB200DnVecSetClosingBarrier", L.lib().aclsparseB200DnVecSetClosingBarrier(
+            self._d, c_void_p(int(local_state)), peer_states, world, rank, spin_limit))
+
     def close(self) -> None:
         if self._d:
             L.lib().aclsparseDestroyDnVec(self._d)
@@ -169,6 +175,12 @@ class DnMat:
         """Device addresses (ints) of buffers that receive every element SpMM writes to this matrix."""
         arr = (c_void_p * max(len(pointers), 1))(*[int(p) for p in pointers])
         check("aclsparseB200DnMatSetMirrors", L.lib().aclsparseB200DnMatSetMirrors(self._d, len(pointers), arr))
+
+    def set_closing_barrier(self, local_state: int, peer_states, world: int, rank: int, spin_limit: int = 0) -> None:
+        """Ends every SpMM into this matrix with the node barrier (aclsparseB200DnMatSetClosingBarrier);
+        ``world <= 1`` removes it.  ``peer_states``: a ctypes array of ``world`` device addresses."""
+        check("aclsparseB200DnMatSetClosingBarrier", L.lib().aclsparseB200DnMatSetClosingBarrier(
+            self._d, c_void_p(int(local_state)), peer_states, world, rank, spin_limit))
 
     def set_multicast_mirror(self, pointer: int) -> None:
         """NVLink multicast address that receives (on every GPU bound to it) each element SpMM writes."""

@@ -73,7 +73,50 @@ aclsparseStatus_t SetMulticastMirror(Descr* d, uint32_t signature, void* multica
     return st;
 }
 
+template <typename Descr>
+aclsparseStatus_t SetClosingBarrier(Descr* d, uint32_t signature, void* localState, void* const* peerStates, int world,
+                                    int rank, unsigned spinLimit)
+{
+    if (d == nullptr || d->signature != signature) {
+        return ACL_SPARSE_STATUS_INVALID_VALUE;
+    }
+    if (localState == nullptr || world <= 1) {
+        d->barrier = AclspBarrierLink{};
+        return ACL_SPARSE_STATUS_SUCCESS;
+    }
+    if (peerStates == nullptr || world > ACLSP_BARRIER_MAX_RANKS || rank < 0 || rank >= world) {
+        return ACL_SPARSE_STATUS_INVALID_VALUE;
+    }
+    AclspBarrierLink link{};
+    for (int r = 0; r < world; ++r) {
+        if (r != rank && peerStates[r] == nullptr) {
+            return ACL_SPARSE_STATUS_INVALID_VALUE;
+        }
+        link.peers[r] = peerStates[r];
+    }
+    link.local = localState;
+    link.world = static_cast<uint32_t>(world);
+    link.rank = static_cast<uint32_t>(rank);
+    link.spinLimit = spinLimit != 0 ? spinLimit : 4000000u;  // about a second, as for aclsparseB200NodeBarrier
+    d->barrier = link;
+    return ACL_SPARSE_STATUS_SUCCESS;
+}
+
 }  // namespace
+
+extern "C" aclsparseStatus_t aclsparseB200DnVecSetClosingBarrier(aclsparseDnVecDescr_t vec, void* localState,
+                                                                 void* const* peerStates, int world, int rank,
+                                                                 unsigned spinLimit)
+{
+    return SetClosingBarrier(vec, kDnVecSignature, localState, peerStates, world, rank, spinLimit);
+}
+
+extern "C" aclsparseStatus_t aclsparseB200DnMatSetClosingBarrier(aclsparseDnMatDescr_t mat, void* localState,
+                                                                 void* const* peerStates, int world, int rank,
+                                                                 unsigned spinLimit)
+{
+    return SetClosingBarrier(mat, kDnMatSignature, localState, peerStates, world, rank, spinLimit);
+}
 
 extern "C" aclsparseStatus_t aclsparseB200DnVecSetMulticastMirror(aclsparseDnVecDescr_t vec, void* multicast)
 {

@@ -27,6 +27,7 @@
 #include <cuda_runtime.h>
 
 #include "aclsparse_b200_kernels.h"
+#include "node_barrier.cuh"
 #include "plan_kernels.h"
 
 namespace {
@@ -71,45 +72,11 @@ struct BarrierPeers {
     AclspNodeBarrierState* ptr[ACLSP_BARRIER_MAX_RANKS];
 };
 
-__device__ __forceinline__ void StoreReleaseSys(uint32_t* addr, uint32_t v)
-{
-    asm volatile("st.release.sys.global.u32 [%0], %1;\n" ::"l"(addr), "r"(v) : "memory");
-}
-
-__device__ __forceinline__ uint32_t LoadAcquireSys(const uint32_t* addr)
-{
-    uint32_t v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(v) : "l"(addr) : "memory");
-    return v;
-}
-
 // One warp; lane r talks to rank r.
 __global__ void NodeBarrierKernel(AclspNodeBarrierState* local, BarrierPeers peers, uint32_t world, uint32_t rank,
                                   uint32_t spinLimit)
 {
-    const uint32_t lane = threadIdx.x;
-    uint32_t epoch = 0;
-    if (lane == 0) {
-        epoch = local->epoch + 1u;
-        local->epoch = epoch;
-    }
-    epoch = __shfl_sync(0xffffffffu, epoch, 0);
-    __threadfence_system();  // the stores of the kernels before this one, to any GPU, come first
-    const bool peer = lane < world && lane != rank;
-    if (peer) {
-        StoreReleaseSys(&peers.ptr[lane]->flag[rank], epoch);
-    }
-    bool arrived = !peer;
-    for (uint32_t spin = 0; spin < spinLimit && !arrived; ++spin) {
-        // Epochs only grow; the difference is compared so that a wrapped counter still orders.
-        arrived = static_cast<int32_t>(LoadAcquireSys(&local->flag[lane]) - epoch) >= 0;
-        if (!arrived) {
-            __nanosleep(64);
-        }
-    }
-    if (!arrived) {
-        atomicExch(&local->status, 1u + lane);  // which peer was missing (the last one to report wins)
-    }
+    aclsp::NodeBarrierWarp(local, reinterpret_cast<void* const*>(peers.ptr), world, rank, spinLimit);
 }
 
 }  // namespace

@@ -10,6 +10,7 @@
 #include <cstddef>
 #include <cstdint>
 
+#include "aclsparse_b200_kernels.h"
 #include "cann_ops_sparse.h"
 
 // Every opaque object starts with a signature word that is checked before any
@@ -139,6 +140,8 @@ struct aclsparseDnVecDescr {
     int numMirrors = 0;
     bool mirrorMulticast = false;
     void* mirrors[7] = {};
+    // aclsparseB200DnVecSetClosingBarrier: the node barrier that ends a product into this vector.
+    AclspBarrierLink barrier = {};
 };
 
 struct aclsparseDnMatDescr {
@@ -155,6 +158,8 @@ struct aclsparseDnMatDescr {
     int numMirrors = 0;
     bool mirrorMulticast = false;
     void* mirrors[7] = {};
+    // aclsparseB200DnMatSetClosingBarrier: the node barrier that ends a product into this matrix.
+    AclspBarrierLink barrier = {};
 };
 
 uint64_t AclspNextWorkspaceOwnerId();

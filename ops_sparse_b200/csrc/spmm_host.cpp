@@ -381,6 +381,9 @@ extern "C" aclsparseStatus_t aclsparseSpMM(aclsparseHandle_t handle, aclsparseOp
         params.alpha = *static_cast<const float*>(alpha);
         params.beta = *static_cast<const float*>(beta);
     }
+    if (params.valueType == ACLSP_TYPE_F32) {
+        params.barrier = matC->barrier;
+    }
     params.numMirrors = static_cast<uint32_t>(matC->numMirrors);
     params.mirrorMulticast = matC->mirrorMulticast ? 1u : 0u;
     for (int m = 0; m < matC->numMirrors; ++m) {

@@ -47,6 +47,7 @@
 
 #include "aclsparse_b200_kernels.h"
 #include "element_types.cuh"
+#include "node_barrier.cuh"
 #include "plan_kernels.h"
 #include "plan_layout.h"
 
@@ -568,6 +569,7 @@ __global__ void SpmmCarryFixupKernel(float* __restrict__ C, SpmmPlanView plan, A
             }
         }
     }
+    aclsp::CloseWithNodeBarrier(p.barrier);  // this is the product's last kernel
 }
 
 template <int VW, bool kStageB>
@@ -642,6 +644,7 @@ extern "C" void spmm_b200_kernel_do(const void* colInd, const void* values, cons
         AclspSpmmParams q = p;
         q.numMirrors = 0;
         q.mirrorMulticast = 0;
+        q.barrier.world = 0;
         if (p.valueType == ACLSP_TYPE_F16) {
             LaunchNarrow<aclsp::kF16>(colInd, values, b, c, plan, q, ds, s);
         } else if (p.valueType == ACLSP_TYPE_BF16) {

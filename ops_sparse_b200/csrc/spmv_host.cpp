@@ -509,6 +509,9 @@ extern "C" aclsparseStatus_t aclsparseSpMV(aclsparseHandle_t handle, aclsparseOp
     if (AclspHostSlotValue(mat->spmv.longestRow, &longest)) {
         params.maxRowLenHint = longest;
     }
+    if (params.valueType == ACLSP_TYPE_F32) {
+        params.barrier = vecY->barrier;
+    }
     params.numMirrors = static_cast<uint32_t>(vecY->numMirrors);
     params.mirrorMulticast = vecY->mirrorMulticast ? 1u : 0u;
     for (int m = 0; m < vecY->numMirrors; ++m) {

@@ -74,6 +74,7 @@
 
 #include "aclsparse_b200_kernels.h"
 #include "element_types.cuh"
+#include "node_barrier.cuh"
 #include "plan_kernels.h"
 #include "plan_layout.h"
 
@@ -996,6 +997,8 @@ SpmvRowBlockKernel(const int32_t* __restrict__ colInd, const float* __restrict__
             atomicAdd(waitFailures, 1u);
         }
     }
+    // p.barrier is set for this kernel only when it is the product's last one (checkPlan == 0).
+    aclsp::CloseWithNodeBarrier(p.barrier);
 }
 
 /* ----------------------------------------------------- carry fix-up -- */
@@ -1006,14 +1009,9 @@ SpmvRowBlockKernel(const int32_t* __restrict__ colInd, const float* __restrict__
 // crossed several tiles are then taken one by one by the whole warp: the lanes add the carry-outs
 // of the tiles the row crossed (lane-strided, then a shuffle tree: a fixed order), lane 0 adds the
 // head partial and writes the row.
-template <int kIn = kF32>
-__global__ void __launch_bounds__(kThreads)
-SpmvCarryFixupKernel(float* __restrict__ y, SpmvPlanView plan, AclspSpmvParams p, const uint32_t* __restrict__ maxRowLen,
-                     uint32_t rowBlockCap)
+template <int kIn>
+__device__ __forceinline__ void JoinCarries(float* __restrict__ y, const SpmvPlanView& plan, const AclspSpmvParams& p)
 {
-    if (rowBlockCap != 0 && *maxRowLen <= rowBlockCap) {
-        return;  // the row-block kernel computed this product: there are no carries
-    }
     const int lane = threadIdx.x & 31;
     const uint32_t warp = blockIdx.x * kWarps + (threadIdx.x >> 5);
     const uint32_t t = warp * 32u + lane;
@@ -1078,6 +1076,19 @@ SpmvCarryFixupKernel(float* __restrict__ y, SpmvPlanView plan, AclspSpmvParams p
             writeRow(row, sum + plan.carry[2 * tt + 1]);
         }
     }
+}
+
+template <int kIn = kF32>
+__global__ void __launch_bounds__(kThreads)
+SpmvCarryFixupKernel(float* __restrict__ y, SpmvPlanView plan, AclspSpmvParams p, const uint32_t* __restrict__ maxRowLen,
+                     uint32_t rowBlockCap)
+{
+    // rowBlockCap != 0 and no longer row: the row-block kernel computed this product, there are no carries;
+    // the closing barrier (this is the product's last kernel) is still this kernel's to run.
+    if (!(rowBlockCap != 0 && *maxRowLen <= rowBlockCap)) {
+        JoinCarries<kIn>(y, plan, p);
+    }
+    aclsp::CloseWithNodeBarrier(p.barrier);
 }
 
 int EnvInt(const char* name, int fallback)
@@ -1152,10 +1163,14 @@ void LaunchProduct(const void* colInd, const void* values, const void* x, void* 
         cap = mean8 <= 8u * 14u ? 16u : (mean8 <= 8u * 28u ? 32u : 0u);
         checkPlan = cap != 0;
     }
+    // The closing barrier of a sharded product belongs to the last kernel launched: the row-block kernel
+    // when it is the only one, else the carry fix-up.
+    AclspSpmvParams inner = p;
+    inner.barrier.world = 0;
     if constexpr (kCanVector) {
         if (cap != 0) {
-            LaunchRowBlocks<kIn>(colInd, values, x, y, plan, p, maxRowLen, waitFailures, static_cast<int>(cap), checkPlan,
-                                 s);
+            LaunchRowBlocks<kIn>(colInd, values, x, y, plan, checkPlan ? inner : p, maxRowLen, waitFailures,
+                                 static_cast<int>(cap), checkPlan, s);
             if (!checkPlan) {
                 return;
             }
@@ -1170,12 +1185,12 @@ void LaunchProduct(const void* colInd, const void* values, const void* x, void* 
     bool launched = false;
     if constexpr (kCanVector) {
         if (vector) {
-            SpmvTileKernel<true, kIn><<<plan.numTiles, kThreads, 0, s>>>(ci, va, xv, yv, plan, p, maxRowLen, tileCap);
+            SpmvTileKernel<true, kIn><<<plan.numTiles, kThreads, 0, s>>>(ci, va, xv, yv, plan, inner, maxRowLen, tileCap);
             launched = true;
         }
     }
     if (!launched) {
-        SpmvTileKernel<false, kIn><<<plan.numTiles, kThreads, 0, s>>>(ci, va, xv, yv, plan, p, maxRowLen, tileCap);
+        SpmvTileKernel<false, kIn><<<plan.numTiles, kThreads, 0, s>>>(ci, va, xv, yv, plan, inner, maxRowLen, tileCap);
     }
     const uint32_t fixupWarps = (plan.numTiles + 31u) / 32u;
     SpmvCarryFixupKernel<kIn><<<(fixupWarps + kWarps - 1u) / kWarps, kThreads, 0, s>>>(yv, plan, p, maxRowLen, tileCap);
@@ -1208,7 +1223,8 @@ extern "C" void spmv_b200_kernel_do(const void* colInd, const void* values, cons
         LaunchProduct<kF32>(colInd, values, x, y, workspace, plan, p, s);
         return;
     }
-    p.numMirrors = 0;  // mirrors of y are for fp32 products
+    p.numMirrors = 0;  // mirrors of y and the closing barrier are for fp32 products
+    p.barrier.world = 0;
     if (p.valueType == ACLSP_TYPE_F16) {
         LaunchProduct<kF16>(colInd, values, x, y, workspace, plan, p, s);
     } else if (p.valueType == ACLSP_TYPE_BF16) {

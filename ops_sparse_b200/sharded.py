@@ -117,6 +117,9 @@ class _PushGather:
         self.barrier_state.zero_()
         state_handle = symm.rendezvous(self.barrier_state, group=group)
         self.barrier_peers = (ctypes.c_void_p * self.world)(*[int(p) for p in state_handle.buffer_ptrs])
+        # True while the product's last kernel ends with the barrier itself (the output descriptor's closing
+        # barrier): run() then launches nothing.
+        self.barrier_in_kernel = False
         torch.cuda.synchronize()
         dist.barrier(group=group)  # every state is zero before any rank announces an epoch
 
@@ -125,6 +128,8 @@ class _PushGather:
             stream = torch.cuda.current_stream().cuda_stream or 0x1
             self._lib.aclsp_b200_push_slice_kernel_do(self.full.data_ptr(), self.peers, self.num_peers, self.offset,
                                                       self.count, stream)
+        if self.barrier_in_kernel:
+            return self.full
         stream = torch.cuda.current_stream().cuda_stream or 0x1
         status = self._lib.aclsparseB200NodeBarrier(stream, self.barrier_state.data_ptr(), self.barrier_peers,
                                                     self.world, self.rank, 0)
@@ -182,6 +187,16 @@ class _GraphedStep:
             self._out.set_multicast_mirror(self.gather.multicast_ptr)
         else:
             self._out.set_mirrors(self.gather.mirror_ptrs)
+        # The step's barrier rides on the product's last kernel whenever this rank launches a product
+        # (a rank without rows launches the barrier kernel instead; ACLSPARSE_SHARDED_FUSED_BARRIER=0:
+        # every rank does, for comparison).
+        fuse = on and self.r1 > self.r0 and os.environ.get("ACLSPARSE_SHARDED_FUSED_BARRIER", "1") != "0"
+        g = self.gather
+        if fuse:
+            self._out.set_closing_barrier(g.barrier_state.data_ptr(), g.barrier_peers, g.world, g.rank)
+        else:
+            self._out.set_closing_barrier(0, None, 0, 0)
+        g.barrier_in_kernel = fuse
 
     def _capture(self, body):
         side = torch.cuda.Stream(device=self.device)

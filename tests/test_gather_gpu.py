@@ -6,10 +6,14 @@ peer-mapped memory.  The multi-rank protocol around it is covered by the 2-rank 
 """
 import ctypes
 
+import numpy as np
 import pytest
 import torch
 
+from oracle import oracle as O
 from ops_sparse_b200 import _lib as L
+from ops_sparse_b200 import api
+from tests.gpu_util import SpmmCase, SpmvCase, random_csr
 
 pytestmark = pytest.mark.gpu
 
@@ -140,3 +144,72 @@ def test_node_barrier_announces_waits_and_gives_up_within_its_limit():
     assert lib.aclsparseB200NodeBarrier(0x1, None, ptrs, world, rank, 0) == L.INVALID_VALUE
     assert lib.aclsparseB200NodeBarrier(0x1, local.data_ptr(), ptrs, 17, rank, 0) == L.INVALID_VALUE
     assert lib.aclsparseB200NodeBarrier(0x1, local.data_ptr(), ptrs, world, 4, 0) == L.INVALID_VALUE
+
+
+@pytest.mark.parametrize("shape", ["row_blocks", "tiles", "spmm"])
+def test_closing_barrier_of_a_product(shape):
+    """The same barrier as the end of a product (aclsparseB200DnVecSetClosingBarrier / DnMat...), on one GPU in
+    the same form: the peers' flags are set by hand before the launch, so nothing waits for another kernel.
+    The product's last kernel (the row-block kernel, the SpMV carry fix-up or the SpMM carry fix-up) announces
+    this rank's epoch to every peer, leaves the CTA ticket counter at zero and the result unchanged; a peer
+    that never arrives makes it give up within its limit, and the product is still right."""
+    lib = L.lib()
+    rng = np.random.default_rng(17)
+    world, rank = 3, 2
+    states = [torch.zeros(32, dtype=torch.int32, device="cuda") for _ in range(world)]
+    ptrs = (ctypes.c_void_p * world)(*[s.data_ptr() for s in states])
+    local = states[rank]
+    missing = ctypes.c_int(-1)
+    rows, cols = 6000, 5000
+    lengths = rng.integers(3, 12, rows) if shape == "row_blocks" else rng.poisson(9, rows)
+    if shape != "row_blocks":
+        lengths[100] = 4500  # a row that crosses tiles: the fix-up kernels have carries to join
+    rp, ci = random_csr(rng, lengths, cols)
+    va = rng.standard_normal(ci.size).astype(np.float32)
+    if shape == "spmm":
+        n = 8
+        b = rng.standard_normal((cols, n)).astype(np.float32)
+        case = SpmmCase(rp, ci, va, cols, n, b, n, np.zeros((rows, n), np.float32), n)
+        truth = O.spmm_f64(rp, ci, va, b, n, np.zeros((rows, n), np.float32), n, n, cols)
+        out = case.mc
+    else:
+        x = rng.standard_normal(cols).astype(np.float32)
+        case = SpmvCase(rp, ci, va, x, np.zeros(rows, np.float32))
+        truth = O.spmv_f64(rp, ci, va, x, np.zeros(rows, np.float32))
+        out = case.vy
+    case.op.preprocess()
+    torch.cuda.synchronize()  # the host knows the longest row: one SpMV kernel (row blocks) or two (tiles)
+
+    def arrive(epoch, ranks):
+        for r in ranks:
+            local[4 + r] = epoch
+        torch.cuda.synchronize()
+
+    def product_ok():
+        got = case.run(preprocess=False).reshape(truth.shape)
+        return O.check_tolerance(got, truth)[0] == 0
+
+    before = api.kernel_launches()
+    assert product_ok()
+    plain_launches = api.kernel_launches() - before
+    out.set_closing_barrier(local.data_ptr(), ptrs, world, rank, 2000)
+    # (1) both peers are there
+    arrive(1, [0, 1])
+    before = api.kernel_launches()
+    assert product_ok()
+    assert api.kernel_launches() - before == plain_launches       # no kernel of its own
+    assert lib.aclsparseB200NodeBarrierStatus(0x1, local.data_ptr(), ctypes.byref(missing)) == L.SUCCESS
+    assert [int(states[r][4 + rank]) for r in (0, 1)] == [1, 1]  # announced to every peer
+    assert int(local[0]) == 1 and int(local[2]) == 0              # epoch counted, tickets back at zero
+    # (2) rank 0 never announces epoch 2: the last CTA gives up after 2000 polls; the product is complete
+    arrive(2, [1])
+    assert product_ok()
+    st = lib.aclsparseB200NodeBarrierStatus(0x1, local.data_ptr(), ctypes.byref(missing))
+    assert st == L.EXECUTION_FAILED and missing.value == 0
+    assert int(states[1][4 + rank]) == 2 and int(local[2]) == 0
+    # (3) the next product, with every peer present, is fine; then the barrier is taken off again
+    arrive(3, [0, 1])
+    assert product_ok()
+    assert lib.aclsparseB200NodeBarrierStatus(0x1, local.data_ptr(), ctypes.byref(missing)) == L.SUCCESS
+    out.set_closing_barrier(0, None, 0, 0)
+    assert product_ok() and int(local[0]) == 3
