@@ -56,8 +56,7 @@ namespace {
 constexpr int kThreads = 256;
 constexpr int kWarps = kThreads / 32;
 constexpr int kTile = ACLSP_SPMM_TILE_ITEMS;
-constexpr int kWarpItems = kTile / kWarps;
-constexpr int kStages = 8;
+constexpr int kMaxStages = 8;
 
 using aclsp::kF32;
 using aclsp::LoadIn;
@@ -176,41 +175,50 @@ __device__ __forceinline__ int LocalMergeRow(const int* sOff, int nr, int nt, in
     return lo;
 }
 
-constexpr size_t SmemBytes(int vw)
+// groups: lane groups per CTA (kThreads / G); a group's ring, tail and head hold G * vw columns, so the
+// sizes of those arrays do not depend on G.
+constexpr size_t SmemBytes(int vw, int groups, int stages)
 {
     return sizeof(int) * (kTile + 2)                    // sOff
            + sizeof(int) * kTile                        // sCol
            + sizeof(float) * kTile                      // sVal
-           + sizeof(float) * kWarps * kStages * 32 * vw // ring
-           + sizeof(double) * 2 * kWarps * 32 * vw      // warp tail / head
-           + sizeof(int) * (2 * kWarps + 2);            // warp row split, head flags
+           + sizeof(float) * kThreads * stages * vw     // rings
+           + sizeof(double) * 2 * kThreads * vw         // group tails / heads
+           + sizeof(int) * (2 * groups + 2);            // group row split, head flags
 }
 
 // kIn != kF32 (narrow storage: fp16, bf16 or int8 values and B, C of type p.cType): `values`, `B` and `C`
 // address elements of those types; only the one-column-per-lane form without staging exists (VW = 1,
 // kStageB = false), which goes through element strides and so covers every layout.
-template <int VW, bool kStageB, int kIn = kF32>
+template <int VW, bool kStageB, int kIn = kF32, int G = 32, int kStages = kMaxStages>
 __global__ void __launch_bounds__(kThreads)
 SpmmTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ values, const float* __restrict__ B,
                float* __restrict__ C, SpmmPlanView plan, AclspSpmmParams p, DenseStrides ds)
 {
     static_assert(kIn == kF32 || (VW == 1 && !kStageB), "narrow storage: one column per lane, no staging");
+    static_assert(G == 32 || G == 16 || G == 8, "lane groups of 8, 16 or 32");
     using V = typename Vec<VW>::T;
-    constexpr int kPanel = 32 * VW;
+    // A lane group is G lanes that walk one piece of the tile together, lane l on columns [l VW, (l+1) VW) of
+    // the pass.  G = 32 is a warp; with narrower C (n <= 64, n <= 32) a warp holds two or four groups, each on
+    // its own piece, so that one warp instruction still serves 32 * VW columns' worth of work.  Below, "warp"
+    // in names and comments means such a group.
+    constexpr int kGroups = kThreads / G;
+    constexpr int kGroupItems = kTile / kGroups;
+    constexpr int kPanel = G * VW;
 
     extern __shared__ __align__(16) unsigned char smemRaw[];
-    double* sTail = reinterpret_cast<double*>(smemRaw);               // [kWarps][kPanel]
-    double* sHead = sTail + kWarps * kPanel;                          // [kWarps][kPanel]
-    float* sRing = reinterpret_cast<float*>(sHead + kWarps * kPanel); // [kWarps][kStages][kPanel]
-    float* sVal = sRing + kWarps * kStages * kPanel;                  // [kTile]
+    double* sTail = reinterpret_cast<double*>(smemRaw);               // [kGroups][kPanel]
+    double* sHead = sTail + kGroups * kPanel;                          // [kGroups][kPanel]
+    float* sRing = reinterpret_cast<float*>(sHead + kGroups * kPanel); // [kGroups][kStages][kPanel]
+    float* sVal = sRing + (kStageB ? kGroups * kStages * kPanel : 0);  // [kTile]; no rings without staging
     int* sCol = reinterpret_cast<int*>(sVal + kTile);                 // [kTile], -1 marks a skipped entry
     int* sOff = sCol + kTile;                                         // [kTile + 2]
-    int* sWarpRow = sOff + kTile + 2;                                 // [kWarps + 1] first local row of each warp
-    int* sHasHead = sWarpRow + kWarps + 1;                            // [kWarps]
+    int* sWarpRow = sOff + kTile + 2;                                 // [kGroups + 1] first local row of each warp
+    int* sHasHead = sWarpRow + kGroups + 1;                            // [kGroups]
 
     const int tid = threadIdx.x;
-    const int lane = tid & 31;
-    const int warp = tid >> 5;
+    const int lane = tid % G;
+    const int warp = tid / G;
     const int t = blockIdx.x;
     const int nnz = static_cast<int>(p.nnz);
     const int n = static_cast<int>(p.n);
@@ -276,8 +284,8 @@ SpmmTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ val
     // This warp's piece of the tile: local rows [r0, r1) end in it, local
     // non-zeros [q0, q1) belong to it.
     const int items = nr + nt;
-    int da = warp * kWarpItems;
-    int db = da + kWarpItems;
+    int da = warp * kGroupItems;
+    int db = da + kGroupItems;
     da = da < items ? da : items;
     db = db < items ? db : items;
     const int r0 = LocalMergeRow(sOff, nr, nt, da);
@@ -288,8 +296,8 @@ SpmmTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ val
     if (lane == 0) {
         sWarpRow[warp] = r0;
         sHasHead[warp] = (headOpen && r1 > r0) ? 1 : 0;
-        if (warp == kWarps - 1) {
-            sWarpRow[kWarps] = r1;
+        if (warp == kGroups - 1) {
+            sWarpRow[kGroups] = r1;
         }
     }
 
@@ -498,15 +506,15 @@ SpmmTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ val
                 storeRow(r0, total);
             }
         }
-        if (warp == kWarps - 1 && colOk) {
-            int firstWarp = kWarps;
+        if (warp == kGroups - 1 && colOk) {
+            int firstWarp = kGroups;
             while (firstWarp > 0 && sWarpRow[firstWarp] == nr) {
                 --firstWarp;
             }
 #pragma unroll
             for (int v = 0; v < VW; ++v) {
                 double sum = 0.0;
-                for (int u = firstWarp; u < kWarps; ++u) {
+                for (int u = firstWarp; u < kGroups; ++u) {
                     sum += sTail[u * kPanel + lane * VW + v];
                 }
                 tileTail[colL + v] = sum;
@@ -572,22 +580,22 @@ __global__ void SpmmCarryFixupKernel(float* __restrict__ C, SpmmPlanView plan, A
     aclsp::CloseWithNodeBarrier(p.barrier);  // this is the product's last kernel
 }
 
-template <int VW, bool kStageB>
+template <int VW, bool kStageB, int G, int kStages = kMaxStages>
 void Launch(const void* colInd, const void* values, const void* b, void* c, const SpmmPlanView& plan,
             const AclspSpmmParams& p, const DenseStrides& ds, cudaStream_t s)
 {
-    constexpr size_t smem = SmemBytes(VW);
+    constexpr size_t smem = SmemBytes(VW, kThreads / G, kStageB ? kStages : 0);
     // More than 48 KiB of dynamic shared memory has to be requested per kernel
     // and per device; the attribute is cheap to set, so it is set every time.
-    cudaFuncSetAttribute(SpmmTileKernel<VW, kStageB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaFuncSetAttribute(SpmmTileKernel<VW, kStageB, kF32, G, kStages>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                          static_cast<int>(smem));
     AclspCountLaunches(1);
-    SpmmTileKernel<VW, kStageB><<<plan.numTiles, kThreads, smem, s>>>(
+    SpmmTileKernel<VW, kStageB, kF32, G, kStages><<<plan.numTiles, kThreads, smem, s>>>(
         static_cast<const int32_t*>(colInd), static_cast<const float*>(values), static_cast<const float*>(b),
         static_cast<float*>(c), plan, p, ds);
 }
 
-template <int VW>
+template <int VW, int G = 32>
 void LaunchByPrecision(const void* colInd, const void* values, const void* b, void* c, const SpmmPlanView& plan,
                        const AclspSpmmParams& p, const DenseStrides& ds, cudaStream_t s)
 {
@@ -598,10 +606,23 @@ void LaunchByPrecision(const void* colInd, const void* values, const void* b, vo
         const char* e = std::getenv("ACLSPARSE_SPMM_STAGE_B");
         return e == nullptr || e[0] != '0';
     }();
-    if (stage) {
-        Launch<VW, true>(colInd, values, b, c, plan, p, ds, s);
+    // Ring depth (gathers in flight per lane group).  With four columns per lane the rings are the largest
+    // part of a CTA's shared memory and decide how many CTAs an SM holds: four stages (5 CTAs per SM) beat
+    // eight (3 CTAs) on the benchmark configurations, c4 1.55 against 1.69 ms, c5 8.6 against 10.0 ms; two are
+    // no better than four.  ACLSPARSE_SPMM_STAGES=8 / 4 / 2 overrides the choice (read once).
+    static const int stagesEnv = [] {
+        const char* e = std::getenv("ACLSPARSE_SPMM_STAGES");
+        return e == nullptr ? 0 : std::atoi(e);
+    }();
+    const int stages = stagesEnv != 0 ? stagesEnv : (VW == 4 ? 4 : 8);
+    if (stage && stages == 4) {
+        Launch<VW, true, G, 4>(colInd, values, b, c, plan, p, ds, s);
+    } else if (stage && stages == 2) {
+        Launch<VW, true, G, 2>(colInd, values, b, c, plan, p, ds, s);
+    } else if (stage) {
+        Launch<VW, true, G, 8>(colInd, values, b, c, plan, p, ds, s);
     } else {
-        Launch<VW, false>(colInd, values, b, c, plan, p, ds, s);
+        Launch<VW, false, G>(colInd, values, b, c, plan, p, ds, s);
     }
 }
 
@@ -609,7 +630,7 @@ template <int kIn>
 void LaunchNarrow(const void* colInd, const void* values, const void* b, void* c, const SpmmPlanView& plan,
                   const AclspSpmmParams& p, const DenseStrides& ds, cudaStream_t s)
 {
-    constexpr size_t smem = SmemBytes(1);
+    constexpr size_t smem = SmemBytes(1, kWarps, 0);
     cudaFuncSetAttribute(SpmmTileKernel<1, false, kIn>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                          static_cast<int>(smem));
     AclspCountLaunches(2);
@@ -660,6 +681,31 @@ extern "C" void spmm_b200_kernel_do(const void* colInd, const void* values, cons
         addr |= static_cast<uintptr_t>(p.mirrorDelta[m]);  // a mirror is as aligned as C and its distance from C
     }
     int vw = 1;
+    // ACLSPARSE_SPMM_LANE_GROUPS=0: always whole warps per piece (a debugging aid, read once).
+    static const bool groups = [] {
+        const char* e = std::getenv("ACLSPARSE_SPMM_LANE_GROUPS");
+        return e == nullptr || e[0] != '0';
+    }();
+    const bool quads = unit && p.n % 4 == 0 && p.ldb % 4 == 0 && p.ldc % 4 == 0 && addr % 16 == 0;
+    auto fixup = [&]() {
+        uint32_t fixupBlocks = (plan.numTiles + 7u) / 8u;
+        fixupBlocks = fixupBlocks > 148u * 8u ? 148u * 8u : fixupBlocks;
+        AclspCountLaunches(1);
+        SpmmCarryFixupKernel<kF32><<<fixupBlocks, 256, 0, s>>>(static_cast<float*>(c), plan, p, ds);
+    };
+    if (quads && groups && p.n <= 64) {
+        // Narrow C: four columns per lane and as few lanes per piece as cover a row of C in one pass (n <= 32:
+        // 8 lanes, n <= 64: 16), so that a warp instruction works on four or two non-zeros at once.  (Eight
+        // columns per lane were measured too: slower, c5 12.7 against 10.5 ms, c4 1.95 against 1.83 ms - the
+        // doubled rings halve the resident CTAs.)
+        if (p.n <= 32) {
+            LaunchByPrecision<4, 8>(colInd, values, b, c, plan, p, ds, s);
+        } else {
+            LaunchByPrecision<4, 16>(colInd, values, b, c, plan, p, ds, s);
+        }
+        fixup();
+        return;
+    }
     if (unit && p.n % 4 == 0 && p.n >= 128 && p.ldb % 4 == 0 && p.ldc % 4 == 0 && addr % 16 == 0) {
         vw = 4;
     } else if (unit && p.n % 2 == 0 && p.n >= 64 && p.ldb % 2 == 0 && p.ldc % 2 == 0 && addr % 8 == 0) {

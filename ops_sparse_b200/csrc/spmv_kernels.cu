@@ -554,6 +554,80 @@ SpmvTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ val
         sOff[k] = ClampOffset(plan.rowPtr[i0 + k], nnz) - j0;
     }
 
+    if constexpr (kVector && kIn == kF32) {
+        if (nr == 0) {
+            // The tile lies inside one row (a power-law row longer than a tile): no product needs to be
+            // staged.  Each thread adds the products of its vectors in registers, in vector order; the
+            // warps are joined in warp order: a fixed order, like every other path.
+            const int nvec = span >> 2;
+            double h = 0.0;
+            float l = 0.0f;
+            constexpr int kDepth = 2;  // vectors (eight gathers) in flight per thread
+            for (int v0 = tid; v0 < nvec; v0 += kDepth * kThreads) {
+                int4 c[kDepth];
+                float4 w[kDepth];
+#pragma unroll
+                for (int u = 0; u < kDepth; ++u) {
+                    const int v = v0 + u * kThreads;
+                    const int e = a0 + 4 * v;
+                    if (v < nvec && e + 4 <= nnz) {
+                        c[u] = __ldcs(reinterpret_cast<const int4*>(colInd + e));
+                        w[u] = __ldcs(reinterpret_cast<const float4*>(values + e));
+                    } else {
+                        int32_t cc[4];
+                        float ww[4];
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            const bool in = v < nvec && e + q < nnz;
+                            cc[q] = in ? __ldcs(colInd + e + q) : -1;
+                            ww[q] = in ? __ldcs(values + e + q) : 0.0f;
+                        }
+                        c[u] = make_int4(cc[0], cc[1], cc[2], cc[3]);
+                        w[u] = make_float4(ww[0], ww[1], ww[2], ww[3]);
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < kDepth; ++u) {
+                    const int e = a0 + 4 * (v0 + u * kThreads);
+                    const int cc[4] = {c[u].x, c[u].y, c[u].z, c[u].w};
+                    const float ww[4] = {w[u].x, w[u].y, w[u].z, w[u].w};
+                    float hi[4];
+                    float lo[4];
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        // elements of the first and last vector that belong to a neighbouring tile do not count
+                        const bool mine = e + q >= j0 && e + q < j1;
+                        Product(ww[q], mine ? cc[q] : -1, x, p.indexBase, p.cols, 1, hi[q], lo[q]);
+                    }
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        h += static_cast<double>(hi[q]);
+                        l += lo[q];
+                    }
+                }
+            }
+            double sum = h + static_cast<double>(l);
+            for (int o = 16; o > 0; o >>= 1) {
+                sum += __shfl_xor_sync(0xffffffffu, sum, o);
+            }
+            if ((tid & 31) == 0) {
+                scratch.warp[tid >> 5] = sum;
+            }
+            __syncthreads();
+            if (tid == 0) {
+                double total = 0.0;
+#pragma unroll
+                for (int wq = 0; wq < kWarps; ++wq) {
+                    total += scratch.warp[wq];
+                }
+                if (!Finite(total)) {
+                    total = ExactSum<kIn>(colInd, values, x, j0, j1, 1, 1, 1, p.indexBase, p.cols);
+                }
+                plan.carry[2 * t] = total;  // the tile's open tail; there is no head piece (no row ends here)
+            }
+            return;
+        }
+    }
     if constexpr (kVector && kIn != kF32) {
         // Eight 2-byte values and eight column indices per step: one 128-bit load of the values, two
         // of the indices; elements of the first and last vector that belong to a neighbouring tile
