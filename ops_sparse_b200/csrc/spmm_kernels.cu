@@ -183,7 +183,7 @@ constexpr size_t SmemBytes(int vw, int groups, int stages)
            + sizeof(int) * kTile                        // sCol
            + sizeof(float) * kTile                      // sVal
            + sizeof(float) * kThreads * stages * vw     // rings
-           + sizeof(double) * 2 * kThreads * vw         // group tails / heads
+           + sizeof(double) * kThreads * vw * (stages >= 2 ? 1 : 2)  // group heads; tails unless they fit the rings
            + sizeof(int) * (2 * groups + 2);            // group row split, head flags
 }
 
@@ -191,6 +191,8 @@ constexpr size_t SmemBytes(int vw, int groups, int stages)
 // address elements of those types; only the one-column-per-lane form without staging exists (VW = 1,
 // kStageB = false), which goes through element strides and so covers every layout.
 template <int VW, bool kStageB, int kIn = kF32, int G = 32, int kStages = kMaxStages>
+// (No minimum of resident CTAs is asked of the compiler: held to 48 registers for five CTAs per SM the
+// four-stage instance was slower than with the 57 it takes by itself, c4 1.67 against 1.55 ms.)
 __global__ void __launch_bounds__(kThreads)
 SpmmTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ values, const float* __restrict__ B,
                float* __restrict__ C, SpmmPlanView plan, AclspSpmmParams p, DenseStrides ds)
@@ -207,9 +209,15 @@ SpmmTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ val
     constexpr int kPanel = G * VW;
 
     extern __shared__ __align__(16) unsigned char smemRaw[];
-    double* sTail = reinterpret_cast<double*>(smemRaw);               // [kGroups][kPanel]
-    double* sHead = sTail + kGroups * kPanel;                          // [kGroups][kPanel]
-    float* sRing = reinterpret_cast<float*>(sHead + kGroups * kPanel); // [kGroups][kStages][kPanel]
+    // With staging, a group's tail (what it hands to the row that continues past it) is written after its walk
+    // into the first half of its own ring, which nothing uses any more by then: the rings are most of the
+    // CTA's shared memory, and shared memory decides how many CTAs an SM holds.
+    constexpr bool kTailInRing = kStageB && kStages >= 2;
+    constexpr int kTailStride = kTailInRing ? kStages * kPanel / 2 : kPanel;  // doubles between two groups' tails
+    double* sHead = reinterpret_cast<double*>(smemRaw);                // [kGroups][kPanel]
+    double* sTailOwn = sHead + kGroups * kPanel;                       // [kGroups][kPanel] unless kTailInRing
+    float* sRing = reinterpret_cast<float*>(sTailOwn + (kTailInRing ? 0 : kGroups * kPanel)); // [kGroups][kStages][kPanel]
+    double* sTail = kTailInRing ? reinterpret_cast<double*>(sRing) : sTailOwn;
     float* sVal = sRing + (kStageB ? kGroups * kStages * kPanel : 0);  // [kTile]; no rings without staging
     int* sCol = reinterpret_cast<int*>(sVal + kTile);                 // [kTile], -1 marks a skipped entry
     int* sOff = sCol + kTile;                                         // [kTile + 2]
@@ -302,6 +310,7 @@ SpmmTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ val
     }
 
     const Scalars sc = LoadScalars(p);
+    const uint32_t bRow32 = static_cast<uint32_t>(ds.bRow);  // strides are positive and below 2^31 (host check)
     const aclsp::TypedScalars tsc = aclsp::LoadTypedScalars(p.computeInt, p.alphaPtr, p.betaPtr, p.alpha, p.beta,
                                                             p.alphaInt, p.betaInt);
     (void)tsc;
@@ -327,7 +336,9 @@ SpmmTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ val
         auto issue = [&](int q) {
             const int c = sCol[q];
             if (c >= 0 && colOk) {
-                CpAsync<4 * VW>(ring + (q % kStages) * kPanel, bLane + static_cast<int64_t>(c) * ds.bRow);
+                // (a row index and a leading dimension both fit 31 bits: one 32 x 32 -> 64 bit multiply)
+                CpAsync<4 * VW>(ring + (static_cast<unsigned>(q) % kStages) * kPanel,
+                                bLane + static_cast<uint64_t>(static_cast<uint32_t>(c)) * bRow32);
             }
             CpAsyncCommit();
         };
@@ -418,7 +429,8 @@ SpmmTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ val
                 CpAsyncWait<kStages - 1>();
                 const int c = sCol[q];
                 if (c >= 0 && colOk) {
-                    accumulate(sVal[q], *reinterpret_cast<const V*>(ring + (q % kStages) * kPanel));
+                    accumulate(sVal[q],
+                               *reinterpret_cast<const V*>(ring + (static_cast<unsigned>(q) % kStages) * kPanel));
                 }
                 if (q + kStages < q1) {
                     issue(q + kStages);
@@ -470,13 +482,14 @@ SpmmTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ val
             flush(row);
             ++row;
         }
+        CpAsyncWait<0>();  // this lane's copies have landed ...
+        __syncwarp();      // ... and every lane of the warp has read what it needed from the rings
         if (colOk) {  // what is left belongs to the row that continues past this warp
 #pragma unroll
             for (int v = 0; v < VW; ++v) {
-                sTail[warp * kPanel + lane * VW + v] = acc[v];
+                sTail[warp * kTailStride + lane * VW + v] = acc[v];
             }
         }
-        CpAsyncWait<0>();
         __syncthreads();
 
         // Rows shared between warps: add the tails of the warps the row
@@ -491,7 +504,7 @@ SpmmTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ val
             for (int v = 0; v < VW; ++v) {
                 double sum = 0.0;
                 for (int u = firstWarp; u < warp; ++u) {
-                    sum += sTail[u * kPanel + lane * VW + v];
+                    sum += sTail[u * kTailStride + lane * VW + v];
                 }
                 total[v] = sum + sHead[warp * kPanel + lane * VW + v];
             }
@@ -515,7 +528,7 @@ SpmmTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ val
             for (int v = 0; v < VW; ++v) {
                 double sum = 0.0;
                 for (int u = firstWarp; u < kGroups; ++u) {
-                    sum += sTail[u * kPanel + lane * VW + v];
+                    sum += sTail[u * kTailStride + lane * VW + v];
                 }
                 tileTail[colL + v] = sum;
             }
