@@ -381,6 +381,56 @@ def test_mirror_list_validation(lib):
     assert lib.aclsparseDestroySpMat(csr) == L.SUCCESS
 
 
+def test_dtype_tables(lib, handle):
+    """The supported element-type combinations are the reference's tables without the complex rows
+    (sparse/spmv/arch35/spmv_host.cpp:44-66, sparse/spmm/arch35/host/spmm_host.cpp:379-387); everything else is
+    NOT_SUPPORTED at the buffer-size query already."""
+    F, H, B, I8, I32, C = L.ACL_FLOAT, L.ACL_FLOAT16, L.ACL_BF16, L.ACL_INT8, L.ACL_INT32, L.ACL_COMPLEX64
+    size = c_size_t(0)
+    spmv_ok = {(F, F, F, F), (H, H, H, F), (H, H, F, F), (B, B, B, F), (B, B, F, F), (I8, I8, F, F), (I8, I8, I32, I32)}
+    spmm_ok = {(F, F, F, F), (H, H, H, F), (H, H, F, F), (B, B, B, F), (B, B, F, F), (I8, I8, I32, I32)}
+    types = (F, H, B, I8, I32, C)
+    for a in types:
+        for xb in types:
+            for yc in types:
+                for ct in (F, I32, C):
+                    mat = make_csr(lib, rows=4, cols=3, nnz=5, dtype=a)
+                    x, y = make_vec(lib, 3, dtype=xb), make_vec(lib, 4, FAKE[4], dtype=yc)
+                    want = L.SUCCESS if (a, xb, yc, ct) in spmv_ok else L.NOT_SUPPORTED
+                    got = lib.aclsparseSpMVGetBufferSize(*spmv_args(handle, mat, x, y, ctype=ct), byref(size))
+                    assert got == want, ("spmv", a, xb, yc, ct, got)
+                    b, c = make_mat(lib, 3, 2, 2, dtype=xb), make_mat(lib, 4, 2, 2, values=FAKE[6], dtype=yc)
+                    want = L.SUCCESS if (a, xb, yc, ct) in spmm_ok else L.NOT_SUPPORTED
+                    got = lib.aclsparseSpMMGetBufferSize(*spmm_args(handle, mat, b, c, ctype=ct), byref(size))
+                    assert got == want, ("spmm", a, xb, yc, ct, got)
+                    for d, destroy in ((mat, lib.aclsparseDestroySpMat), (x, lib.aclsparseDestroyDnVec),
+                                       (y, lib.aclsparseDestroyDnVec), (b, lib.aclsparseDestroyDnMat),
+                                       (c, lib.aclsparseDestroyDnMat)):
+                        assert destroy(d) == L.SUCCESS
+
+
+def test_closing_barrier_validation(lib):
+    """aclsparseB200Dn{Vec,Mat}SetClosingBarrier: argument checks; world <= 1 or a NULL state clears it."""
+    vec, mat = make_vec(lib, 8), make_mat(lib, 4, 4, 4)
+    peers = (c_void_p * 4)(*[FAKE[i].value for i in range(4)])
+    holed = (c_void_p * 4)(FAKE[0].value, None, FAKE[2].value, FAKE[3].value)
+    for setter, good, other in ((lib.aclsparseB200DnVecSetClosingBarrier, vec, mat),
+                                (lib.aclsparseB200DnMatSetClosingBarrier, mat, vec)):
+        assert setter(good, FAKE[8], peers, 4, 1, 0) == L.SUCCESS
+        assert setter(good, FAKE[8], holed, 4, 1, 0) == L.SUCCESS        # the rank's own entry is not used
+        assert setter(good, FAKE[8], holed, 4, 0, 0) == L.INVALID_VALUE  # a peer's entry is
+        assert setter(good, FAKE[8], None, 4, 1, 0) == L.INVALID_VALUE
+        assert setter(good, FAKE[8], peers, 17, 1, 0) == L.INVALID_VALUE
+        assert setter(good, FAKE[8], peers, 4, 4, 0) == L.INVALID_VALUE
+        assert setter(good, FAKE[8], peers, 4, -1, 0) == L.INVALID_VALUE
+        assert setter(good, None, None, 0, 0, 0) == L.SUCCESS            # cleared
+        assert setter(good, FAKE[8], peers, 1, 0, 0) == L.SUCCESS        # one rank: nothing to wait for
+        assert setter(None, FAKE[8], peers, 4, 1, 0) == L.INVALID_VALUE
+        assert setter(other, FAKE[8], peers, 4, 1, 0) == L.INVALID_VALUE  # wrong descriptor kind
+    assert lib.aclsparseDestroyDnVec(vec) == L.SUCCESS
+    assert lib.aclsparseDestroyDnMat(mat) == L.SUCCESS
+
+
 def test_create_destroy_loop(lib):
     """Descriptor churn does not accumulate state (the reference's leak loop, spmv_test.cpp:1710-1738)."""
     for _ in range(2000):
