@@ -180,8 +180,7 @@ __device__ __forceinline__ int LocalMergeRow(const int* sOff, int nr, int nt, in
 constexpr size_t SmemBytes(int vw, int groups, int stages)
 {
     return sizeof(int) * (kTile + 2)                    // sOff
-           + sizeof(int) * kTile                        // sCol
-           + sizeof(float) * kTile                      // sVal
+           + sizeof(int2) * kTile                       // sColVal
            + sizeof(float) * kThreads * stages * vw     // rings
            + sizeof(double) * kThreads * vw * (stages >= 2 ? 1 : 2)  // group heads; tails unless they fit the rings
            + sizeof(int) * (2 * groups + 2);            // group row split, head flags
@@ -218,9 +217,10 @@ SpmmTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ val
     double* sTailOwn = sHead + kGroups * kPanel;                       // [kGroups][kPanel] unless kTailInRing
     float* sRing = reinterpret_cast<float*>(sTailOwn + (kTailInRing ? 0 : kGroups * kPanel)); // [kGroups][kStages][kPanel]
     double* sTail = kTailInRing ? reinterpret_cast<double*>(sRing) : sTailOwn;
-    float* sVal = sRing + (kStageB ? kGroups * kStages * kPanel : 0);  // [kTile]; no rings without staging
-    int* sCol = reinterpret_cast<int*>(sVal + kTile);                 // [kTile], -1 marks a skipped entry
-    int* sOff = sCol + kTile;                                         // [kTile + 2]
+    // [kTile] (column, value bits) of every non-zero, column -1 for a skipped entry: one load serves both.
+    // (No rings without staging.)
+    int2* sColVal = reinterpret_cast<int2*>(sRing + (kStageB ? kGroups * kStages * kPanel : 0));
+    int* sOff = reinterpret_cast<int*>(sColVal + kTile);               // [kTile + 2]
     int* sWarpRow = sOff + kTile + 2;                                 // [kGroups + 1] first local row of each warp
     int* sHasHead = sWarpRow + kGroups + 1;                            // [kGroups]
 
@@ -281,8 +281,7 @@ SpmmTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ val
                 const int k = g + q - j0;
                 if (k >= 0 && k < nt) {
                     const uint32_t col = static_cast<uint32_t>(c[q]) - p.indexBase;
-                    sCol[k] = col < p.cols ? static_cast<int>(col) : -1;
-                    sVal[k] = w[q];
+                    sColVal[k] = make_int2(col < p.cols ? static_cast<int>(col) : -1, __float_as_int(w[q]));
                 }
             }
         }
@@ -334,7 +333,7 @@ SpmmTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ val
             acc[v] = 0.0;
         }
         auto issue = [&](int q) {
-            const int c = sCol[q];
+            const int c = sColVal[q].x;
             if (c >= 0 && colOk) {
                 // (a row index and a leading dimension both fit 31 bits: one 32 x 32 -> 64 bit multiply)
                 CpAsync<4 * VW>(ring + (static_cast<unsigned>(q) % kStages) * kPanel,
@@ -420,22 +419,45 @@ SpmmTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ val
                     CpAsyncCommit();
                 }
             }
-            for (int q = q0; q < q1; ++q) {
-                while (rowEnd <= q && row < r1) {
-                    flush(row);
-                    ++row;
-                    rowEnd = row < nr ? sOff[row + 1] : nt + 1;
-                }
+            // One non-zero: wait for its row of B, add it in, start the copy kStages non-zeros ahead.
+            auto step = [&](int q) {
                 CpAsyncWait<kStages - 1>();
-                const int c = sCol[q];
-                if (c >= 0 && colOk) {
-                    accumulate(sVal[q],
+                const int2 cv = sColVal[q];
+                if (cv.x >= 0 && colOk) {
+                    accumulate(__int_as_float(cv.y),
                                *reinterpret_cast<const V*>(ring + (static_cast<unsigned>(q) % kStages) * kPanel));
                 }
                 if (q + kStages < q1) {
                     issue(q + kStages);
                 } else {
                     CpAsyncCommit();
+                }
+            };
+            if (nt >= 8 * (nr + 1)) {
+                // Rows of eight non-zeros and more on average: walk to the next row end without a test per
+                // non-zero (measured on c4, rows of 16: 1.47 against 1.60 ms).
+                int q = q0;
+                while (q < q1) {
+                    while (rowEnd <= q && row < r1) {
+                        flush(row);
+                        ++row;
+                        rowEnd = row < nr ? sOff[row + 1] : nt + 1;
+                    }
+                    const int stop = (row < r1 && rowEnd < q1) ? rowEnd : q1;  // no row ends before it
+                    for (; q < stop; ++q) {
+                        step(q);
+                    }
+                }
+            } else {
+                // Short rows: the inner loop above would be entered and left every few non-zeros (measured on
+                // c5: 9.5 against 9.1 ms), so the row end is tested with every non-zero.
+                for (int q = q0; q < q1; ++q) {
+                    while (rowEnd <= q && row < r1) {
+                        flush(row);
+                        ++row;
+                        rowEnd = row < nr ? sOff[row + 1] : nt + 1;
+                    }
+                    step(q);
                 }
             }
         } else {
@@ -447,9 +469,10 @@ SpmmTileKernel(const int32_t* __restrict__ colInd, const float* __restrict__ val
 #pragma unroll
                 for (int u = 0; u < kUnroll; ++u) {
                     const int qq = q + u;
-                    const int c = qq < q1 ? sCol[qq] : -1;
+                    const int2 cv = qq < q1 ? sColVal[qq] : make_int2(-1, 0);
+                    const int c = cv.x;
                     const bool ok = c >= 0 && colOk;
-                    a[u] = ok ? sVal[qq] : 0.0f;
+                    a[u] = ok ? __int_as_float(cv.y) : 0.0f;
                     if constexpr (kIn != kF32) {
                         *reinterpret_cast<float*>(&b[u]) =
                             ok ? LoadIn<kIn>(B, static_cast<int64_t>(colL) * ds.bCol + static_cast<int64_t>(c) * ds.bRow)
