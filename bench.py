@@ -434,17 +434,33 @@ def measure(ctx: Context, args, cfg: dict, steps: int, warmup: int, min_warm_sec
         host_in = op.pinned_input_share(cfg)
         host_out = torch.empty_like(out0[op.r0:op.r1]).pin_memory()
         e_steps = max(1, min(steps, 3 if not spmv else steps))
+        # The result goes back on a copy stream of its own, so that the download of step i and the upload of
+        # step i + 1 share the (full-duplex) host link; events keep the order: a download starts after its
+        # product, and the next product, which overwrites y / C, starts after the download.
+        main = torch.cuda.current_stream()
+        copy_stream = torch.cuda.Stream(device=device)
+        downloaded = None
         ctx.barrier()
         for it in range(1 + e_steps):
             if it == 1:
+                main.wait_stream(copy_stream)
                 ctx.barrier()
                 t0 = torch.cuda.Event(enable_timing=True)
                 t1 = torch.cuda.Event(enable_timing=True)
                 t0.record()
             op.load_input_share(host_in)
+            if downloaded is not None:
+                main.wait_event(downloaded)
             reset_output()
             result = op.step(alpha, beta)
-            host_out.copy_(result[op.r0:op.r1].view(host_out.shape), non_blocking=True)
+            computed = torch.cuda.Event()
+            computed.record(main)
+            with torch.cuda.stream(copy_stream):
+                copy_stream.wait_event(computed)
+                host_out.copy_(result[op.r0:op.r1].view(host_out.shape), non_blocking=True)
+                downloaded = torch.cuda.Event()
+                downloaded.record(copy_stream)
+        main.wait_stream(copy_stream)  # the last download is inside the timed region
         t1.record()
         ctx.barrier()
         e_ms = ctx.max_over_ranks(t0.elapsed_time(t1)) / e_steps
@@ -452,9 +468,10 @@ def measure(ctx: Context, args, cfg: dict, steps: int, warmup: int, min_warm_sec
         d2h = int(ctx.sum_over_ranks(float(host_out.numel() * 4)))
         e2e = {"value": workloads.flops(cfg) / (e_ms * 1e-3) / 1e9, "unit": "GFLOP/s", "h2d_bytes_per_step": h2d,
                "d2h_bytes_per_step": d2h, "ms_per_step": e_ms, "steps": e_steps,
-               "what": "per rank: its share of x (or B) pinned host -> device, all-gather of the shares into the "
-                       "replicas, the sharded product step, its own row block of y (or C) -> pinned host; A "
-                       "resident; bytes are summed over ranks"}
+               "what": "per rank and step: its share of x (or B) pinned host -> device, all-gather of the shares "
+                       "into the replicas, the sharded product step, its own row block of y (or C) -> pinned host "
+                       "on a copy stream, so that one step's download overlaps the next step's upload; every "
+                       "copy of every step is inside the timed region; A resident; bytes are summed over ranks"}
         del host_in, host_out
     except (RuntimeError, ValueError, TypeError) as err:  # the same on every rank: none is left waiting
         e2e = None

@@ -1042,12 +1042,34 @@ SpmvRowBlockKernel(const int32_t* __restrict__ colInd, const float* __restrict__
                 }
                 q += kUnroll;
             }
-            if (rowOk) {
-                double sum = h + static_cast<double>(l);
-                if (!Finite(sum)) {
-                    sum = ExactSum<kIn>(colInd, values, x, static_cast<int64_t>(g.a0) + b,
-                                        static_cast<int64_t>(g.a0) + e, 1, 1, 1, p.indexBase, p.cols);
+            double sum = h + static_cast<double>(l);
+            if (rowOk && !Finite(sum)) {
+                sum = ExactSum<kIn>(colInd, values, x, static_cast<int64_t>(g.a0) + b, static_cast<int64_t>(g.a0) + e,
+                                    1, 1, 1, p.indexBase, p.cols);
+            }
+            // With mirrors, a full block whose 32 results start on a 16-byte boundary everywhere goes out as
+            // eight 16-byte vectors (lanes 0 - 7, four neighbours' results each) instead of 32 words: the links
+            // carry packets four times as large.
+            bool vectorMirrors = false;
+            if (kIn == kF32 && p.numMirrors != 0) {
+                vectorMirrors = g.nrows == kBlockRows && p.yStride == 1 &&
+                                (reinterpret_cast<uintptr_t>(y + r0) & 15u) == 0;
+                for (uint32_t m = 0; m < p.numMirrors; ++m) {
+                    vectorMirrors = vectorMirrors && (p.mirrorDelta[m] & 15) == 0;
                 }
+            }
+            if (vectorMirrors) {
+                float* at = y + row;
+                const float out = StoreRow(at, row, sum, sc, p);
+                float4 v;
+                v.x = __shfl_sync(0xffffffffu, out, 4 * (lane & 7));
+                v.y = __shfl_sync(0xffffffffu, out, 4 * (lane & 7) + 1);
+                v.z = __shfl_sync(0xffffffffu, out, 4 * (lane & 7) + 2);
+                v.w = __shfl_sync(0xffffffffu, out, 4 * (lane & 7) + 3);
+                if (lane < 8) {
+                    MirrorStore(reinterpret_cast<float4*>(y + r0 + 4 * lane), v, p);
+                }
+            } else if (rowOk) {
                 writeRow(row, sum);
             }
         }

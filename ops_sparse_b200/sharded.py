@@ -61,6 +61,19 @@ def shard_csr(row_ptr: np.ndarray, col_ind: np.ndarray, values: np.ndarray, boun
     return local_ptr, col_ind[p0:p1], values[p0:p1]
 
 
+def align_bounds(bounds: np.ndarray, multiple: int) -> np.ndarray:
+    """The inner boundaries of a row partition moved to the nearest multiple of ``multiple`` rows (the ends stay):
+    every rank's block of a result vector then starts on a 128-byte boundary for ``multiple`` = 32, which lets the
+    product kernels send their rows to the other GPUs as whole 16-byte vectors.  The balance by non-zeros moves
+    by at most ``multiple`` / 2 rows per boundary."""
+    out = np.asarray(bounds, dtype=np.int64).copy()
+    rows = int(out[-1])
+    for g in range(1, out.size - 1):
+        moved = int(round(int(out[g]) / multiple)) * multiple
+        out[g] = min(max(moved, int(out[g - 1])), rows)
+    return out.astype(np.int32)
+
+
 class _Gather:
     """All-gather of unequal row blocks: padded slots, then one concatenation."""
 
@@ -308,7 +321,7 @@ class ShardedSpMV(_GraphedStep):
         self.algorithm = "exact fp32 products (hi + lo), fp64 row sums"
         self.kernel_names = "SpmvRowBlockKernel + SpmvTileKernel + SpmvCarryFixupKernel"
         base = cfg.get("index_base", 0)
-        self.bounds = row_block_bounds_host(cfg["row_ptr"], cfg["nnz"], world, base)
+        self.bounds = align_bounds(row_block_bounds_host(cfg["row_ptr"], cfg["nnz"], world, base), 32)
         self.local_ptr, self.local_col, self.local_val = shard_csr(cfg["row_ptr"], cfg["col_ind"], cfg["values"],
                                                                    self.bounds, rank, base)
         self.r0, self.r1 = int(self.bounds[rank]), int(self.bounds[rank + 1])

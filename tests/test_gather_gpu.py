@@ -55,12 +55,15 @@ def test_graph_replay_of_a_step_equals_the_eager_step(name):
     assert torch.equal(op.step(1.0, 0.0), op.step(1.0, 0.0))  # other scalars: eager path, still valid
 
 
-@pytest.mark.parametrize("name,beta", [("c1", 0.0), ("c1", 0.5), ("c3", 0.5), ("c4", 0.0), ("c4", -0.25)])
+@pytest.mark.parametrize("name,beta,pad", [("c1", 0.0, 5), ("c1", 0.5, 5), ("c3", 0.5, 5), ("c4", 0.0, 5),
+                                           ("c4", -0.25, 5), ("c2", 0.0, 5), ("c2", 0.5, 8), ("c2", 0.0, 8)])
 @pytest.mark.parametrize("mirrors", [1, 7])
-def test_mirrors_receive_exactly_what_the_output_receives(name, beta, mirrors):
-    """Every element the product writes lands in each mirror too, bit for bit; nothing else is touched."""
+def test_mirrors_receive_exactly_what_the_output_receives(name, beta, pad, mirrors):
+    """Every element the product writes lands in each mirror too, bit for bit; nothing else is touched.  pad: guard
+    elements either side of each mirror; 5 also puts the mirrors off 16-byte alignment (word stores), 8 keeps them
+    on it (the row-block kernel of c2 then sends 16-byte vectors; 29791 rows: the last block is partial)."""
     from ops_sparse_b200 import api, workloads
-    cfg = workloads.make(name, rows={"c1": None, "c3": 40000, "c4": 6000}[name])
+    cfg = workloads.make(name, rows={"c1": None, "c2": 29791, "c3": 40000, "c4": 6000}[name])
     dev = torch.device("cuda:0")
     spmv = cfg["kind"] == "spmv"
     rows, cols = cfg["rows"], cfg["cols"]
@@ -68,7 +71,6 @@ def test_mirrors_receive_exactly_what_the_output_receives(name, beta, mirrors):
     mat = api.CsrMatrix(rows, cols, torch.from_numpy(cfg["row_ptr"]).to(dev), torch.from_numpy(cfg["col_ind"]).to(dev),
                         torch.from_numpy(cfg["values"]).to(dev), 0, nnz=cfg["nnz"])
     out0 = torch.from_numpy(cfg["y"] if spmv else cfg["c"]).to(dev)
-    pad = 5  # guard elements either side of each mirror; also puts the mirrors off 16-byte alignment
     def run(with_mirrors):
         out = out0.clone()
         bufs = [torch.full((out.numel() + 2 * pad,), 7.0, device=dev) for _ in range(mirrors if with_mirrors else 0)]
