@@ -129,6 +129,11 @@ template <int BYTES>
 __device__ __forceinline__ void CpAsync(void* smem, const void* gmem)
 {
     const unsigned dst = static_cast<unsigned>(__cvta_generic_to_shared(smem));
+    if constexpr (BYTES == 16) {
+        // A gathered row of B is used once by this CTA: keep it out of L1 (the .cg form exists for 16 bytes only).
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(gmem) : "memory");
+        return;
+    }
     asm volatile("cp.async.ca.shared.global [%0], [%1], %2;\n" ::"r"(dst), "l"(gmem), "n"(BYTES) : "memory");
 }
 
