@@ -79,6 +79,13 @@ aclsparseStatus_t aclsparseB200NodeBarrier(aclrtStream stream, void* localState,
                                            int rank, unsigned spinLimit);
 aclsparseStatus_t aclsparseB200NodeBarrierStatus(aclrtStream stream, void* localState, int* missingRank);
 
+/* How many warps of SpMV products over the plan in `externalBuffer` gave up waiting for a bulk copy since the
+ * plan was built (the SpMV row-block kernel waits for its copies at most about a quarter of a second each; a
+ * warp whose wait runs out computes its remaining rows with plain loads, so the results are right either way,
+ * and counts itself here).  Synchronises `stream` and reads the counter from the plan header.  A diagnostic:
+ * anything but 0 means the copy engine did not deliver in time.  No counterpart in the reference. */
+aclsparseStatus_t aclsparseB200SpMVWaitFailures(aclrtStream stream, const void* externalBuffer, unsigned* count);
+
 /* The same barrier as the END of every product written into `vec` / `mat`, instead of a kernel of its own:
  * the last kernel of aclsparseSpMV / aclsparseSpMM (fp32) runs it in the CTA that finishes last, after
  * that CTA has seen all others fence their stores, so a sharded step is the product kernels alone.  The

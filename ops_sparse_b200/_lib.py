@@ -181,6 +181,7 @@ SIGNATURES = {
     "aclsparseB200DnMatSetMulticastMirror": [_P, _P],
     "aclsparseB200NodeBarrier": [_P, _P, POINTER(c_void_p), c_int, c_int, c_uint32],
     "aclsparseB200NodeBarrierStatus": [_P, _P, POINTER(c_int)],
+    "aclsparseB200SpMVWaitFailures": [_P, _P, POINTER(c_uint32)],
     "aclsparseB200DnVecSetClosingBarrier": [_P, _P, POINTER(c_void_p), c_int, c_int, c_uint32],
     "aclsparseB200DnMatSetClosingBarrier": [_P, _P, POINTER(c_void_p), c_int, c_int, c_uint32],
     # include/aclsparse_b200_kernels.h

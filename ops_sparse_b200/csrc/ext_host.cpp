@@ -6,6 +6,7 @@
 #include "aclsparse_b200_ext.h"
 #include "aclsparse_b200_kernels.h"
 #include "internal.h"
+#include "plan_layout.h"
 
 extern "C" aclsparseStatus_t aclsparseB200RowBlockBounds(aclsparseHandle_t handle, aclsparseConstSpMatDescr_t matA,
                                                          int parts, void* bounds)
@@ -162,6 +163,24 @@ extern "C" aclsparseStatus_t aclsparseB200NodeBarrier(aclrtStream stream, void* 
         ACLSP_LOGE("aclsparseB200NodeBarrier", "kernel enqueue failed");
         return ACL_SPARSE_STATUS_EXECUTION_FAILED;
     }
+    return ACL_SPARSE_STATUS_SUCCESS;
+}
+
+extern "C" aclsparseStatus_t aclsparseB200SpMVWaitFailures(aclrtStream stream, const void* externalBuffer,
+                                                           unsigned* count)
+{
+    if (externalBuffer == nullptr || count == nullptr) {
+        return ACL_SPARSE_STATUS_INVALID_VALUE;
+    }
+    auto s = static_cast<cudaStream_t>(stream);
+    uint32_t value = 0;
+    const auto* at = static_cast<const unsigned char*>(externalBuffer) + ACLSP_HEADER_WAIT_FAILURES_OFF;
+    if (cudaMemcpyAsync(&value, at, sizeof(value), cudaMemcpyDeviceToHost, s) != cudaSuccess ||
+        cudaStreamSynchronize(s) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return ACL_SPARSE_STATUS_EXECUTION_FAILED;
+    }
+    *count = value;
     return ACL_SPARSE_STATUS_SUCCESS;
 }
 

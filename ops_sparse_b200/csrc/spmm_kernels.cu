@@ -1,28 +1,34 @@
 /*
- * CSR SpMM for sm_100a:  C = alpha * A * op(B) + beta * C,  fp32, int32 indices.
+ * CSR SpMM for sm_100a:  C = alpha * A * op(B) + beta * C,  int32 indices, fp32 (and narrow storage types).
  *
  * No tensor cores: at 16-32 non-zeros per row the product is a gather of rows
- * of B, bound by memory, not a dense contraction.
+ * of B, not a dense contraction.
  *
  * Work decomposition.  As for SpMV the matrix is cut along the merge path of
  * (row ends, non-zeros), here into tiles of 1024 items, one CTA per tile, and
- * the CTA cuts its tile once more the same way into eight 128-item pieces, one
- * per warp.  A warp therefore streams at most 128 non-zeros whatever the row
- * lengths are: a 500 000-entry row is spread over thousands of warps and a run
- * of empty rows costs as much as a run of non-zeros.
- *   1. The CTA stages the tile's column indices and values in shared memory
- *      with coalesced 128-bit loads (evict-first).
- *   2. Each warp walks its non-zeros in order.  For every non-zero the lanes
- *      copy one row of B (a 32*VW-column panel of it) into the warp's ring of
- *      shared-memory stages with cp.async, kStages rows ahead of the FMAs, so
- *      eight row gathers per warp are in flight while earlier rows are
- *      multiplied.  A lane reads back only the bytes it copied itself, so the
- *      ring needs no barrier, only cp.async.wait_group.
+ * the CTA cuts its tile once more the same way into equal pieces, one per
+ * LANE GROUP.  A group is a warp (eight 128-item pieces) when C has 128
+ * columns or more; for narrower C it is as few lanes as cover a row of C in
+ * one pass (16 lanes for n <= 64, 8 for n <= 32), so that one warp instruction
+ * works on two or four non-zeros.  A group streams at most its piece whatever
+ * the row lengths are: a 500 000-entry row is spread over thousands of groups
+ * and a run of empty rows costs as much as a run of non-zeros.
+ *   1. The CTA stages (column, value) of the tile's non-zeros as one word
+ *      pair each in shared memory, from coalesced 128-bit loads (evict-first).
+ *   2. Each group walks its non-zeros in order.  For every non-zero the lanes
+ *      copy one row of B (G*VW columns of it) into the group's ring of
+ *      shared-memory stages with cp.async (.cg for 16-byte pieces: a row is
+ *      used once), kStages rows ahead of the FMAs.  A lane reads back only the
+ *      bytes it copied itself, so the ring needs no barrier, only
+ *      cp.async.wait_group.  Four stages with four columns per lane: the
+ *      rings are most of a CTA's shared memory, and resident CTAs matter more
+ *      than depth (the kernel is bound on the SM side, not by DRAM).
  *   3. At a row end the accumulators are written as alpha*acc + beta*C.  The
- *      piece of a row that a warp shares with its neighbours goes to shared
- *      memory and is combined in warp order; the pieces a tile shares with its
- *      neighbours go to the plan's carry area and are combined in tile order
- *      by a second kernel.  All orders are fixed: results are reproducible.
+ *      piece of a row that a group shares with its neighbours goes to shared
+ *      memory and is combined in group order; the pieces a tile shares with
+ *      its neighbours go to the plan's carry area and are combined in tile
+ *      order by a second kernel.  All orders are fixed: results are
+ *      reproducible.
  *
  * Accuracy.  Products and row sums are fp64 (exact products of fp32 factors,
  * which cannot overflow), alpha * sum + beta * C is evaluated in fp64 and
@@ -35,6 +41,10 @@
  * addresses aligned to the vector).  VW = 1 addresses both matrices through
  * (row stride, column stride) pairs and so also covers column-major B / C and
  * op(B) = transpose.
+ *
+ * Element types.  fp16 / bf16 / int8 values and B with C of the same type,
+ * fp32 or (int8) saturating int32 run the VW = 1 form without staging on typed
+ * loads and stores (element_types.cuh); their products are exact in fp64 too.
  *
  * Out-of-range input never faults: offsets are clamped and entries whose
  * column falls outside [0, k) are skipped (reference:

@@ -1,5 +1,6 @@
 /*
- * CSR SpMV for sm_100a:  y = alpha * A * x + beta * y,  fp32 data, int32 indices.
+ * CSR SpMV for sm_100a:  y = alpha * A * x + beta * y,  int32 indices, fp32 data (and the narrow storage
+ * types of element_types.cuh: typed instances of the same kernels, exact products without the error term).
  *
  * Two kernels.  The preprocessing pass records the longest row of the matrix in
  * the plan header and sends a copy to pinned host memory, asynchronously.  Once
@@ -23,7 +24,9 @@
  *    consecutive rows at the same position, so for banded matrices their
  *    gathers fall into one or two lines of x.  Every wait is bounded; a warp
  *    whose wait runs out stops using the copy engine and finishes its blocks
- *    with plain loads, so the product is still right.
+ *    with plain loads, so the product is still right.  With mirrors (a sharded
+ *    product) the 32 results of a block go to the other GPUs straight from
+ *    registers, as eight 16-byte vectors when the block is aligned.
  *
  * B. Merge-path tiles (SpmvTileKernel), for everything else.  The matrix is cut
  *    along the merge path of (row ends, non-zeros) into tiles of kTile items, so
@@ -45,6 +48,8 @@
  *      carry-out, and the piece of a row that began in an earlier tile becomes
  *      its head partial; a second small kernel adds the carries of a split row
  *      in tile order and writes that row.
+ *    A tile that lies inside one row (rows longer than a tile) skips staging:
+ *    its products are added in registers, the warps joined in warp order.
  * Every sum is taken in a fixed order, so results are bit-reproducible.
  *
  * Accuracy.  Every product is kept exactly (hi + lo, rounded product and its

@@ -431,6 +431,12 @@ def test_closing_barrier_validation(lib):
     assert lib.aclsparseDestroyDnMat(mat) == L.SUCCESS
 
 
+def test_wait_failure_counter_validation(lib):
+    count = ctypes.c_uint32(7)
+    assert lib.aclsparseB200SpMVWaitFailures(STREAM, None, byref(count)) == L.INVALID_VALUE
+    assert lib.aclsparseB200SpMVWaitFailures(STREAM, FAKE[0], None) == L.INVALID_VALUE
+
+
 def test_create_destroy_loop(lib):
     """Descriptor churn does not accumulate state (the reference's leak loop, spmv_test.cpp:1710-1738)."""
     for _ in range(2000):

@@ -16,6 +16,17 @@ from oracle import oracle as O
 from ops_sparse_b200 import sharded, workloads
 
 
+def test_aligned_bounds_keep_the_partition_valid():
+    """Inner boundaries move to multiples of 32 rows (so that every rank's block of y starts on a 128-byte
+    boundary); the ends stay, the order stays, ranks may end up without rows."""
+    for raw in ([0, 1000, 2047, 2049, 5000], [0, 3, 5, 9], [0, 10, 20, 40], [0, 16, 48, 49], [0, 0, 0, 7]):
+        got = sharded.align_bounds(np.array(raw, np.int32), 32)
+        assert got.dtype == np.int32 and got[0] == raw[0] and got[-1] == raw[-1]
+        assert np.all(np.diff(got) >= 0)
+        assert all(int(b) % 32 == 0 or int(b) == raw[-1] for b in got[1:-1])
+        assert np.all(np.abs(got[1:-1].astype(np.int64) - np.array(raw[1:-1])) <= 32)
+
+
 def test_bounds_match_the_oracle_twin():
     rng = np.random.default_rng(2)
     for lens in (rng.poisson(16, 5000), np.clip(rng.zipf(2.0, 4000), 1, 2000), np.zeros(100, int),

@@ -137,6 +137,10 @@ def test_both_kernels_agree_and_no_wait_runs_out():
         "    got = case.run(cfg['alpha'], cfg['beta'])\n"
         "    fails = int(case.op.buffer[128:132].view(torch.int32).item())\n"
         "    assert fails == 0, fails\n"
+        "    import ctypes; from ops_sparse_b200 import _lib as L\n"
+        "    count = ctypes.c_uint32(9)\n"
+        "    st = L.lib().aclsparseB200SpMVWaitFailures(0x1, case.op.buffer.data_ptr(), ctypes.byref(count))\n"
+        "    assert st == L.SUCCESS and count.value == 0, (st, count.value)\n"
         "    out.append(got)\n"
         "np.save(sys.argv[1], np.concatenate(out))\n"
     ) % (os.path.dirname(os.path.abspath(__file__)), os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
