@@ -177,3 +177,49 @@ def test_oracle_against_live_reference():
         np.testing.assert_array_equal(r, r2)
         np.testing.assert_array_equal(e, e2)
         assert (ident, uni) == (ident2, uni2)
+
+
+def test_narrow_roundings_are_single_and_to_nearest_even():
+    """The oracle's fp64 -> bf16 / fp16 conversions (what the narrow-type GPU results are compared with) against
+    exact rational arithmetic: nearest bf16 / fp16 value, ties to even, including values a hair off a tie, where a
+    detour through fp32 rounds the wrong way.  int8 -> int32: exact integers, saturated."""
+    from fractions import Fraction
+    rng = np.random.default_rng(12)
+
+    def nearest(v, values):
+        """Index of the value nearest to v in the ascending list `values`, ties to the even index."""
+        lo, hi = 0, len(values) - 1
+        a = Fraction(float(v))
+        while hi - lo > 1:
+            mid = (lo + hi) // 2
+            if values[mid] <= a:
+                lo = mid
+            else:
+                hi = mid
+        dl, dh = a - values[lo], values[hi] - a
+        return lo if dl < dh or (dl == dh and lo % 2 == 0) else hi
+
+    # all positive finite bf16 values from 2^-20 to 2^20, as exact fractions
+    bits = np.arange(0x3580, 0x4980, dtype=np.uint16)
+    grid = [Fraction(float(f)) for f in O.bf16_bits_to_f32(bits)]
+    base = np.array([float(g) for g in grid[:-1]])
+    mid = (base + np.array([float(g) for g in grid[1:]])) / 2          # exact: one more bit
+    probes = np.concatenate([rng.uniform(float(grid[0]), float(grid[-1]), 300), mid[::16],
+                             mid[::16] * (1 + 2.0 ** -40), mid[::16] * (1 - 2.0 ** -40)])
+    got = O.f64_to_bf16_bits(probes)
+    want = np.array([bits[nearest(v, grid)] for v in probes], dtype=np.uint16)
+    assert np.array_equal(got, want)
+    assert np.array_equal(O.f64_to_bf16_bits(-probes), want | np.uint16(0x8000))
+    # fp16 the same way, around 1.0
+    hbits = np.arange(0x3800, 0x4000, dtype=np.uint16)
+    hgrid = [Fraction(float(f)) for f in hbits.view(np.float16)]
+    hmid = np.array([float((a + b) / 2) for a, b in zip(hgrid[:-1], hgrid[1:])])
+    hprobes = np.concatenate([hmid[::8], hmid[::8] * (1 + 2.0 ** -40), hmid[::8] * (1 - 2.0 ** -40)])
+    assert np.array_equal(O.f64_to_f16(hprobes).view(np.uint16),
+                          np.array([hbits[nearest(v, hgrid)] for v in hprobes], dtype=np.uint16))
+    # the reference's own known answers (test/spmv/arch35/spmv_test.cpp:665-697): 1 + 2^-11 -> 1 in fp16
+    assert O.f64_to_f16(np.array([1 + 2.0 ** -11, -(1 + 2.0 ** -11)])).view(np.uint16).tolist() == [0x3C00, 0xBC00]
+    # int8 x int8 -> int32 with saturation (test/spmv/arch35/spmv_test.cpp:617-663)
+    got = O.spmv_i8_i32([0, 1, 2, 2], [0, 1], np.array([127, -127], np.int8), np.array([127, 127], np.int8),
+                        np.zeros(3, np.int32), 2 ** 31 - 1, 0)
+    assert got.tolist() == [2 ** 31 - 1, -2 ** 31, 0]
