@@ -445,6 +445,26 @@ def test_create_destroy_loop(lib):
         assert lib.aclsparseDestroyDnVec(x) == L.SUCCESS
 
 
+def test_public_headers_are_plain_c(tmp_path):
+    """The boundary is a C ABI: the three public headers compile as C99 with no C++ and no CUDA in sight, and the
+    parameter blocks have the sizes the ctypes mirrors in ops_sparse_b200/_lib.py assume."""
+    import shutil
+    import subprocess
+    if shutil.which("gcc") is None:
+        pytest.skip("no C compiler")
+    src = tmp_path / "abi.c"
+    src.write_text(
+        '#include <stdio.h>\n#include "cann_ops_sparse.h"\n#include "aclsparse_b200_ext.h"\n'
+        '#include "aclsparse_b200_kernels.h"\n'
+        'int main(void) { printf("%zu %zu %zu %zu\\n", sizeof(AclspSpmvParams), sizeof(AclspSpmmParams), '
+        'sizeof(AclspBarrierLink), sizeof(AclspNodeBarrierState)); return 0; }\n')
+    exe = tmp_path / "abi"
+    subprocess.run(["gcc", "-std=c99", "-Wall", "-Wextra", "-pedantic", "-Werror", "-I", os.path.join(ROOT, "include"),
+                    str(src), "-o", str(exe)], check=True)
+    sizes = [int(v) for v in subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.split()]
+    assert sizes == [ctypes.sizeof(L.SpmvParams), ctypes.sizeof(L.SpmmParams), ctypes.sizeof(L.BarrierLink), 80]
+
+
 def test_library_exports_only_its_c_api():
     """Hidden visibility: the dynamic symbol table holds the C entry points and nothing else of this library."""
     import subprocess
